@@ -29,7 +29,7 @@ from typing import List, Optional
 import numpy as np
 import torch
 
-from ..parts.base import KVCacheNeed, LayerCache, StateNeed
+from ..parts.base import KVCacheNeed, LayerCache, StateNeed, flatten_needs
 from .page_pool import PagePool
 from .state_slots import StateSlots
 
@@ -72,20 +72,23 @@ class CacheManager:
         self.state_groups: List[_Group] = []
         self.layer_caches: List[Optional[LayerCache]] = [None] * len(needs)
         by_need = {}
+        step_kv = {}                                     # step -> (group index, position in the group)
+        step_states = {}                                 # step -> [state group, ...] in the order the step declared them
         for step, need in enumerate(needs):
-            if need is None:
-                continue
-            if isinstance(need, KVCacheNeed):
-                g = by_need.get(need)
-                if g is None:
-                    g = by_need[need] = _Group(need, [])
-                    self.kv_groups.append(g)
-                g.steps.append(step)
-            elif isinstance(need, StateNeed):
-                g = _Group(need, [step])
-                self.state_groups.append(g)
-            else:
-                raise TypeError(f"execution step {step}: unknown cache need {need!r}")
+            for n in flatten_needs(need):                # a step may own pages AND one or more states
+                if isinstance(n, KVCacheNeed):
+                    g = by_need.get(n)
+                    if g is None:
+                        g = by_need[n] = _Group(n, [])
+                        self.kv_groups.append(g)
+                    step_kv[step] = (g, len(g.steps))
+                    g.steps.append(step)
+                elif isinstance(n, StateNeed):
+                    g = _Group(n, [step])
+                    self.state_groups.append(g)
+                    step_states.setdefault(step, []).append(g)
+                else:
+                    raise TypeError(f"execution step {step}: unknown cache need {n!r}")
         for gi, g in enumerate(self.kv_groups):
             g.pool = PagePool(num_pages)
             g.tables = np.zeros((max_seqs + 1, self.max_pages_per_seq), dtype=np.int32)
@@ -101,17 +104,20 @@ class CacheManager:
                 else:
                     g.storage = torch.zeros((len(g.steps), n.planes, num_pages + 1, n.num_kv_heads, page_size, n.head_dim),
                                             dtype=dtype, device=self.device)
-            for j, step in enumerate(g.steps):
+        for g in self.state_groups:
+            if allocate:
+                sd = {"compute": dtype, "int32": torch.int32}.get(g.need.dtype, torch.float32)
+                g.storage = torch.zeros((max_seqs + 1, *g.need.shape), dtype=sd, device=self.device)
+        for step in sorted(set(step_kv) | set(step_states)):
+            gi, k, v = -1, None, None
+            if step in step_kv:
+                g, j = step_kv[step]
+                gi = self.kv_groups.index(g)
                 k = g.storage[j, 0] if allocate else None
                 v = g.storage[j, 1] if allocate and g.need.planes > 1 and g.value_storage is None else None
                 if allocate and g.value_storage is not None:
                     v = g.value_storage[j]
-                self.layer_caches[step] = LayerCache(gi, k=k, v=v)
-        for g in self.state_groups:
-            if allocate:
-                sd = dtype if g.need.dtype == "compute" else torch.float32
-                g.storage = torch.zeros((max_seqs + 1, *g.need.shape), dtype=sd, device=self.device)
-            self.layer_caches[g.steps[0]] = LayerCache(-1, state=g.storage)
+            self.layer_caches[step] = LayerCache(gi, k=k, v=v, states=[g.storage for g in step_states.get(step, [])])
 
     # ---------------------------------------------------------------- sizes
     @property
@@ -128,7 +134,7 @@ class CacheManager:
     def state_bytes_per_seq(self) -> int:
         """Bytes of fixed-size state one live request occupies over all state groups."""
         el = torch.empty((), dtype=self.dtype).element_size()
-        return sum(math.prod(g.need.shape) * (el if g.need.dtype == "compute" else 4) for g in self.state_groups)
+        return sum(math.prod(g.need.shape) * (el if g.need.dtype == "compute" else 4) for g in self.state_groups)     # float32 and int32: 4
 
     def pages_for(self, num_tokens: int) -> int:
         return math.ceil(num_tokens / self.page_size)

@@ -94,6 +94,12 @@ class ModelSpec:
     # "compute": the residual stream has the run's dtype; "float32": it is kept in 32 bits whatever the run's dtype
     # (the norms of such a model read and write a float32 stream and hand rows of the run's dtype to the parts)
     residual: str = "compute"
+    # a part of the "embedding" family that turns token ids into the first rows of the stream (None: a plain lookup in the
+    # embedding table); its tensors are named by embedding_part_names ((part tensor, checkpoint name) pairs); it may keep state
+    embedding_part: Optional[PartSpec] = None
+    embedding_part_names: Tuple[Tuple[str, str], ...] = ()
+    # logits <- cap * tanh(logits / cap) (None: the head's product as it is)
+    logit_softcap: Optional[float] = None
 
     def __post_init__(self):
         for i, step in enumerate(self.order):

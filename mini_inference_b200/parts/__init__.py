@@ -1,4 +1,4 @@
-from . import attention, block, latent_attention, mlp, norm, recurrent, rope, sink_attention  # noqa: F401  (register the built-in parts)
+from . import attention, block, embedding, filters, latent_attention, mlp, norm, parallel, recurrent, rope, sink_attention  # noqa: F401  (register the built-in parts)
 from .base import (KVCacheNeed, LayerCache, Part, StateNeed, StepContext, WeightSpec, build_part, lookup,
                    register_block, register_feed_forward, register_mixer, register_norm, register_position)
 from .model import DecoderModel

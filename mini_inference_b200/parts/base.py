@@ -20,10 +20,16 @@ Interfaces
   Mixer        cache_need() -> KVCacheNeed | StateNeed | None
                forward(h, ctx, cache, position, owns_cache) -> [T, hidden]
                    cache is the LayerCache of the execution step (or of the step it reads)
+  Embedding    cache_need() -> StateNeed | None
+               forward(ids, table, ctx, cache) -> float32 stream [T, hidden] (the model's embedding table is handed in)
+  InputFilter  cache_need() -> StateNeed | None;  forward(h, ctx, state) -> rows of the same shape
+  ResidualGate forward(h, ctx) -> (logits [T, hidden], bias [hidden]): the sublayer's output is multiplied by sigmoid(logits + bias)
   Block        roles = {role: family}    the parts it arranges; the model builds one part per role from
                                          LayerSpec.parts and hands them over as a dict
                __init__(spec, parts)
                mixer                     the part whose cache_need() the cache manager serves
+               cache_need()              (optional) the step's whole need when parts other than the mixer keep state too:
+                                         a tuple of needs; the step's LayerCache then carries the slot tensors in that order
                forward(x, delta, ctx, cache, owns_cache) -> (x, delta)
                    x is the residual stream, delta an addition not yet applied to it
 
@@ -93,15 +99,45 @@ class KVCacheNeed:
 class StateNeed:
     """Fixed-size per-request state, one slot per live request, zeroed when claimed."""
     shape: Tuple[int, ...]
-    dtype: str = "float32"          # "float32" or "compute"
+    dtype: str = "float32"          # "float32", "int32" or "compute"
+
+
+def flatten_needs(need):
+    """A cache need may be None, one need, or a tuple of needs (a mixer that keeps pages AND a state; a block whose own
+    parts keep state beside the mixer's): the needs in order, at most one of them a KVCacheNeed."""
+    if need is None:
+        return ()
+    if isinstance(need, (tuple, list)):
+        out = tuple(n for part in need for n in flatten_needs(part))
+        if sum(isinstance(n, KVCacheNeed) for n in out) > 1:
+            raise ValueError("an execution step can own the pages of one cache group only")
+        return out
+    return (need,)
+
+
+class GatedDelta:
+    """An addition to the residual stream that is still to be gated: the stream receives sigmoid(logits + bias) * (y + y_bias),
+    element by element (y_bias: a vector added to every row of y first, or None).  Only norms that declare
+    takes_gated_delta understand it; a block hands it to the next norm, whose kernel applies it in float32."""
+    __slots__ = ("y", "logits", "bias", "y_bias")
+
+    def __init__(self, y, logits, bias, y_bias=None):
+        self.y, self.logits, self.bias, self.y_bias = y, logits, bias, y_bias
 
 
 class LayerCache:
     """What one execution step's mixer gets from the cache manager: for pages, the step's key
     and value pools [pages, kv_heads, page_size, head_dim] and the index of the cache group
     whose block tables (ctx.batch.group_view(group, ...)) address them; for state, the slot tensor."""
-    def __init__(self, group: int, k=None, v=None, state=None):
-        self.group, self.k, self.v, self.state = group, k, v, state
+    def __init__(self, group: int, k=None, v=None, state=None, states=None):
+        self.group, self.k, self.v = group, k, v
+        # a step that declared several StateNeeds finds their slot tensors in `states`, in the order it declared them
+        self.states = tuple(states) if states is not None else (() if state is None else (state,))
+        self.state = state if state is not None else (self.states[0] if self.states else None)
+
+    def only(self, pages: bool, states):
+        """The view a sub-part gets: the pages (or none) and the given slice of the state tensors."""
+        return LayerCache(self.group if pages else -1, self.k if pages else None, self.v if pages else None, states=self.states[states])
 
 
 class StepContext:
@@ -134,6 +170,9 @@ class Part:
     accepts_deferred = False
     takes_next_weight = False
     keeps_float32_stream = False     # Norm: reads and writes a float32 residual stream whatever the run's dtype, takes pre_add=
+    takes_gated_delta = False        # Norm: `delta` may be a GatedDelta, applied to the stream in the norm's kernel
+    owns_state = False               # Block: cache_need() gives the step's whole need (its own parts' state beside the mixer's)
+    offers_unbiased = False          # FeedForward: forward_unbiased(h, ctx) -> (y, bias): forward == y + bias, the addition left to the caller
     step_arrays_key: Optional[str] = None
 
     def first_product_probe(self, ops, rows):
@@ -151,6 +190,11 @@ class Part:
     def step_arrays(self, facts):
         return {}
 
+    def subparts(self):
+        """Parts this part is composed of (a mixer made of two mixers): the model looks through them for weights to time,
+        work to count and per-step arrays, as it does through the block's own parts."""
+        return []
+
     def step_flops(self, rows: int, pairs: int) -> int:
         """Floating-point operations beyond the part's matrix products, for `rows` tokens that see `pairs`
         (query, key) pairs (an attention mixer: scores and weighted sum)."""
@@ -158,7 +202,10 @@ class Part:
 
 
 _REGISTRIES: Dict[str, Dict[str, Callable]] = {
-    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}}
+    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {},
+    # embedding: how token ids become the first rows of the stream (beyond a plain table lookup);
+    # input_filter: what a sublayer's input passes before the sublayer reads it; residual_gate: what a sublayer's output is multiplied by
+    "embedding": {}, "input_filter": {}, "residual_gate": {}}
 
 
 def _register(family: str, name: str):
@@ -173,6 +220,9 @@ def register_feed_forward(name): return _register("feed_forward", name)
 def register_norm(name): return _register("norm", name)
 def register_position(name): return _register("position", name)
 def register_block(name): return _register("block", name)
+def register_embedding(name): return _register("embedding", name)
+def register_input_filter(name): return _register("input_filter", name)
+def register_residual_gate(name): return _register("residual_gate", name)
 
 
 def lookup(family: str, name: str):

@@ -9,7 +9,7 @@ with defer=True when every norm of the model accepts deferred sums; a norm that 
 told which weight the following part streams first."""
 from __future__ import annotations
 
-from .base import Part, register_block
+from .base import GatedDelta, Part, StateNeed, flatten_needs, register_block
 
 
 @register_block("prenorm")
@@ -88,3 +88,70 @@ class OutputNormBlock(Part):
 class OutputNormMixerOnly(OutputNormBlock):
     """A layer without feed-forward: x <- x + norm1(mixer(x))."""
     roles = {"mixer": "mixer", "norm1": "norm", "position": "position"}
+
+
+@register_block("gated_prenorm")
+class GatedPreNormBlock(Part):
+    """Pre-norm arrangement whose sublayers read a FILTERED copy of the normed rows and whose outputs are GATED by the
+    unfiltered rows before they join the stream:
+        n = norm1(x);  x <- x + gate1(n) * mixer(filter1(n));   n = norm2(x);  x <- x + gate2(n) * feed_forward(filter2(n)).
+    The stream is float32.  Each gated output travels as a GatedDelta to the next norm, whose kernel applies the gate and adds
+    to the stream in float32.  The filters may keep state of their own: the block declares the step's whole cache need, the
+    mixer's first and the filters' behind it, and hands each part its own piece of the step's LayerCache."""
+    roles = {"mixer": "mixer", "feed_forward": "feed_forward", "norm1": "norm", "norm2": "norm", "position": "position",
+             "filter1": "input_filter", "filter2": "input_filter", "gate1": "residual_gate", "gate2": "residual_gate"}
+    owns_state = True
+
+    def __init__(self, spec, parts):
+        super().__init__(spec)
+        self.parts = dict(parts)
+        self.mixer, self.feed_forward = parts["mixer"], parts.get("feed_forward")
+        self.norm1, self.norm2, self.position = parts["norm1"], parts.get("norm2"), parts["position"]
+        self.filter1, self.filter2 = parts["filter1"], parts.get("filter2")
+        self.gate1, self.gate2 = parts["gate1"], parts.get("gate2")
+        for n in self.norms():
+            if not n.takes_gated_delta:
+                raise ValueError("the gated arrangement needs norms that apply a gated addition (takes_gated_delta)")
+        mixer_needs = flatten_needs(self.mixer.cache_need())
+        self._mixer_states = sum(isinstance(n, StateNeed) for n in mixer_needs)
+        self._needs, at = list(mixer_needs), self._mixer_states
+        self._filter_state = {}
+        for name in ("filter1", "filter2"):
+            f = parts.get(name)
+            if f is not None and f.cache_need() is not None:
+                self._needs.append(f.cache_need())
+                self._filter_state[name] = at
+                at += 1
+
+    def norms(self):
+        return [n for n in (self.norm1, self.norm2) if n is not None]
+
+    def cache_need(self):
+        return tuple(self._needs)
+
+    def _state(self, cache, name):
+        return cache.states[self._filter_state[name]] if name in self._filter_state else None
+
+    def forward(self, x, delta, ctx, cache, owns_cache=True, pre_add=None):
+        if pre_add is not None:
+            raise ValueError("the gated arrangement takes no pass vector")
+        n = self.norm1.forward(x, delta, ctx)
+        logits, bias = self.gate1.forward(n, ctx)
+        y = self.mixer.forward(self.filter1.forward(n, ctx, self._state(cache, "filter1")), ctx,
+                               cache.only(True, slice(0, self._mixer_states)), self.position, owns_cache)
+        a = GatedDelta(y, logits, bias)
+        if self.feed_forward is None:
+            return x, a
+        n = self.norm2.forward(x, a, ctx)
+        logits, bias = self.gate2.forward(n, ctx)
+        h = self.filter2.forward(n, ctx, self._state(cache, "filter2"))
+        if self.feed_forward.offers_unbiased:
+            y, y_bias = self.feed_forward.forward_unbiased(h, ctx)
+            return x, GatedDelta(y, logits, bias, y_bias)
+        return x, GatedDelta(self.feed_forward.forward(h, ctx), logits, bias)
+
+
+@register_block("gated_prenorm_mixer")
+class GatedPreNormMixerOnly(GatedPreNormBlock):
+    """A layer without feed-forward: x <- x + gate1(n) * mixer(filter1(n))."""
+    roles = {"mixer": "mixer", "norm1": "norm", "position": "position", "filter1": "input_filter", "gate1": "residual_gate"}

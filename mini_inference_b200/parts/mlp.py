@@ -91,31 +91,51 @@ class RoutedExperts(Part):
     groups (of `count` equal groups of neighbouring experts) whose best choice score is largest; the chosen experts'
     weights are their plain s, not renormalised.  Expert: g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit),
     y = g * sigmoid(gate_slope * g) * (u + 1), output W_down y.  The token's output is the weighted sum over its experts
-    (added in the order of choice, in float32) plus the shared expert's output."""
+    (added in the order of choice, in float32) plus the shared expert's output.
+
+    Options that other designs set: score="sigmoid" (s = sigmoid(W_r h) per expert instead of the softmax); correction=False (no
+    correction tensor: the choice is made on s itself); act="silu" (an expert is W_down(silu(W_gate h) * W_up h), no clamps);
+    weight_on="input" (a chosen expert's score multiplies its INPUT, out = sum expert(s * h), instead of its output);
+    shared_gate=True (the shared expert's output is multiplied by sigmoid(w_sg . h), one number per token, tensor `shared.sg`;
+    its logit is made in float32 beside the router's)."""
 
     def __init__(self, spec):
         super().__init__(spec)
         g = spec.get
         self.hidden, self.E, self.top, self.F = int(g("hidden_size")), int(g("num_experts")), int(g("top")), int(g("expert_size"))
         self.groups = tuple(g("groups")) if g("groups") else None
-        self.limit, self.slope = float(g("limit")), float(g("gate_slope", 1.702))
+        self.score, self.act, self.weight_on = g("score", "softmax"), g("act", "clamped"), g("weight_on", "output")
+        if self.score not in ("softmax", "sigmoid") or self.act not in ("clamped", "silu") or self.weight_on not in ("output", "input"):
+            raise ValueError("routed_experts: score is softmax or sigmoid, act clamped or silu, weight_on output or input")
+        self.has_correction, self.shared_gate = bool(g("correction", True)), bool(g("shared_gate", False))
+        self.limit = float(g("limit")) if self.act == "clamped" else float("inf")
+        self.slope = float(g("gate_slope", 1.702)) if self.act == "clamped" else 1.0
+        self.up_shift = 1.0 if self.act == "clamped" else 0.0
         self.shared_size = g("shared_size")
-        self.shared_limit = float(g("shared_limit")) if self.shared_size else None
+        self.shared_limit = float(g("shared_limit")) if self.shared_size and self.act == "clamped" else None
+        if self.shared_gate and not self.shared_size:
+            raise ValueError("routed_experts: a shared gate needs a shared expert")
         self.router = self.correction = self.w_in = self.w_out = self.shared_in = self.shared_out = None
 
     def weight_specs(self):
         hid, F = self.hidden, self.F
-        specs = [WeightSpec("router", (self.E, hid)), WeightSpec("correction", (self.E,), kind="vector", init="zeros")]
+        specs = [WeightSpec("router", (self.E, hid))]
+        if self.has_correction:
+            specs.append(WeightSpec("correction", (self.E,), kind="vector", init="zeros"))
         for e in range(self.E):
             specs += [WeightSpec(f"e{e}.gate", (F, hid)), WeightSpec(f"e{e}.up", (F, hid)), WeightSpec(f"e{e}.down", (hid, F))]
         if self.shared_size:
             S = int(self.shared_size)
             specs += [WeightSpec("shared.gate", (S, hid)), WeightSpec("shared.up", (S, hid)), WeightSpec("shared.down", (hid, S))]
+            if self.shared_gate:
+                specs.append(WeightSpec("shared.sg", (1, hid)))
         return specs
 
     def load(self, tensors, dtype, device):
         self.router = tensors.pop("router").contiguous()                   # stored values as they are; products and sums are float32
-        self.correction = tensors.pop("correction").float().contiguous()
+        if self.shared_gate:                                               # the shared gate's row rides behind the experts' rows
+            self.router = torch.cat([self.router, tensors.pop("shared.sg").reshape(1, -1)], dim=0).contiguous()
+        self.correction = tensors.pop("correction").float().contiguous() if self.has_correction else None
         # per expert [gate rows | up rows] and the down matrix, stacked: one grouped product each
         self.w_in = torch.stack([torch.cat([tensors.pop(f"e{e}.gate"), tensors.pop(f"e{e}.up")], dim=0) for e in range(self.E)]).contiguous()
         self.w_out = torch.stack([tensors.pop(f"e{e}.down") for e in range(self.E)]).contiguous()
@@ -132,8 +152,50 @@ class RoutedExperts(Part):
 
     def forward(self, h, ctx):
         ops = ctx.ops
-        chosen, weights = ops.route_topk(h, self.router, self.correction, self.top, self.groups)
+        if self.score == "softmax" and not self.shared_gate:
+            chosen, weights = ops.route_topk(h, self.router, self.correction, self.top, self.groups)
+            extra = None
+        else:
+            chosen, weights, extra = ops.route_topk(h, self.router, self.correction, self.top, self.groups, score=self.score,
+                                                    extra_rows=int(self.shared_gate))
         shared = None
-        if self.shared_size:
+        if self.shared_size and self.act == "clamped":
             shared = ops.linear(ops.clamped_glu(ops.linear(h, self.shared_in), self.shared_limit, self.slope), self.shared_out)
-        return ops.expert_ffn(h, chosen, weights, self.w_in, self.w_out, self.limit, self.slope, shared)
+        elif self.shared_size:
+            shared = ops.linear(ops.gated_linear(h, self.shared_in), self.shared_out)
+        if self.act == "clamped" and self.weight_on == "output" and extra is None:
+            return ops.expert_ffn(h, chosen, weights, self.w_in, self.w_out, self.limit, self.slope, shared)
+        return ops.expert_ffn(h, chosen, weights, self.w_in, self.w_out, self.limit, self.slope, shared, up_shift=self.up_shift,
+                              weight_on_input=self.weight_on == "input", shared_gate=extra)
+
+
+@register_feed_forward("relu2_mlp")
+class SquaredReluMLP(Part):
+    """W_down (relu(W_up h + b_up))^2 + b_down.  The first bias and the activation are one kernel; the second bias is left to
+    whoever adds the output to the stream (forward_unbiased), or added here."""
+    offers_unbiased = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden, self.inter = int(spec.get("hidden_size")), int(spec.get("intermediate_size"))
+        self.up = self.down = self.up_b = self.down_b = None
+
+    def weight_specs(self):
+        return [WeightSpec("up", (self.inter, self.hidden)), WeightSpec("up.b", (self.inter,), kind="vector", init="zeros"),
+                WeightSpec("down", (self.hidden, self.inter)), WeightSpec("down.b", (self.hidden,), kind="vector", init="zeros")]
+
+    def load(self, tensors, dtype, device):
+        self.up, self.down = tensors.pop("up"), tensors.pop("down")
+        self.up_b, self.down_b = tensors.pop("up.b").float().contiguous(), tensors.pop("down.b").float().contiguous()
+
+    @property
+    def first_weight(self):
+        return self.up
+
+    def forward_unbiased(self, h, ctx):
+        ops = ctx.ops
+        return ops.linear(ops.bias_act(ops.linear(h, self.up), self.up_b, "relu2"), self.down), self.down_b
+
+    def forward(self, h, ctx):
+        y, b = self.forward_unbiased(h, ctx)
+        return ctx.ops.bias_act(y, b, "none")

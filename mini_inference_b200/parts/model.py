@@ -44,6 +44,16 @@ class DecoderModel:
             self.blocks.append(block_cls(PartSpec.of(layer.block), parts))
         self.final_norm = build_part("norm", spec.final_norm)
         self.embedding_norm = build_part("norm", spec.embedding_norm) if spec.embedding_norm is not None else None
+        self.embedder = None
+        if spec.embedding_part is not None:
+            if spec.embedding_norm is not None or spec.residual != "float32":
+                raise ValueError("an embedding part starts a float32 stream and takes the place of an embedding norm")
+            self.embedder = build_part("embedding", spec.embedding_part)
+            names = dict(spec.embedding_part_names)
+            for ws in self.embedder.weight_specs():
+                if ws.name not in names:
+                    raise KeyError(f"embedding_part_names has no entry for '{ws.name}'")
+                self._owned.append((names[ws.name], ws, self.embedder))
         norms = [p for b in self.blocks for role, p in b.parts.items() if b.roles[role] == "norm"] + [self.final_norm]
         if self.embedding_norm is not None:
             norms.append(self.embedding_norm)
@@ -59,6 +69,12 @@ class DecoderModel:
         self.pass_vectors = None
         self.dtype = None
         self.device = None
+
+    def _parts_of(self, block):
+        """The block's parts and, behind each, the parts it is composed of."""
+        for part in block.parts.values():
+            yield part
+            yield from part.subparts()
 
     # ---------------------------------------------------------------- weights
     def weight_table(self) -> List[Tuple[str, WeightSpec]]:
@@ -100,7 +116,7 @@ class DecoderModel:
         """The matrices the model multiplies by (after the parts fused what they fuse)."""
         out = []
         for block in self.blocks:
-            for part in block.parts.values():
+            for part in self._parts_of(block):
                 out += [v for v in vars(part).values() if isinstance(v, torch.Tensor) and v.dim() == 2 and v.is_floating_point()]
         out.append(self.lm_head)
         return out
@@ -112,7 +128,7 @@ class DecoderModel:
             return frozenset()
         shapes = set()
         for block in self.blocks:
-            for part in block.parts.values():
+            for part in self._parts_of(block):
                 w = part.open_weight
                 if part.offers_open and isinstance(w, torch.Tensor) and w.dim() == 2:
                     shapes.add((w.shape[0], w.shape[1]))
@@ -122,7 +138,7 @@ class DecoderModel:
         """(N, K) of the matrices that go through ctx.ops.gated_linear."""
         shapes = set()
         for block in self.blocks:
-            for part in block.parts.values():
+            for part in self._parts_of(block):
                 w = part.gated_weight
                 if isinstance(w, torch.Tensor) and w.dim() == 2:
                     shapes.add((w.shape[0], w.shape[1]))
@@ -132,7 +148,7 @@ class DecoderModel:
         """{(N, K) of a part's first weight: probe(rows) -> run(weight)} for the parts that offer one (see Part)."""
         probes = {}
         for block in self.blocks:
-            for part in block.parts.values():
+            for part in self._parts_of(block):
                 w = part.first_weight
                 if isinstance(w, torch.Tensor) and w.dim() == 2 and (w.shape[0], w.shape[1]) not in probes:
                     if part.first_product_probe(ops, 1) is not None:
@@ -144,7 +160,7 @@ class DecoderModel:
         wants logits for `logit_rows` of them: 2 per weight element and row, plus what the mixers report."""
         total = 2 * logit_rows * self.lm_head.numel()
         for step in self.spec.order:
-            for part in self.blocks[step.layer].parts.values():
+            for part in self._parts_of(self.blocks[step.layer]):
                 total += 2 * rows * sum(v.numel() for v in vars(part).values()
                                         if isinstance(v, torch.Tensor) and v.dim() == 2 and v.is_floating_point())
                 total += part.step_flops(rows, pairs)
@@ -154,17 +170,24 @@ class DecoderModel:
         """{key: part.step_arrays} of the parts that ask for per-step arrays of their own, one per key."""
         hooks = {}
         for block in self.blocks:
-            for part in block.parts.values():
+            for part in self._parts_of(block):
                 if part.step_arrays_key is not None:
                     hooks.setdefault(part.step_arrays_key, part.step_arrays)
         return hooks
 
     # ---------------------------------------------------------------- cache needs
     def cache_needs(self):
-        """Per execution step: the mixer's need, or None when the step reads another's cache."""
+        """Per execution step: the mixer's need (the block's, when its own parts keep state too), or None when the step
+        reads another's cache.  An embedding part that keeps state adds one more entry behind the steps'."""
         needs = []
         for step in self.spec.order:
-            needs.append(None if step.cache_from is not None else self.blocks[step.layer].mixer.cache_need())
+            block = self.blocks[step.layer]
+            if step.cache_from is not None:
+                needs.append(None)
+            else:
+                needs.append(block.cache_need() if block.owns_state else block.mixer.cache_need())
+        if self.embedder is not None and self.embedder.cache_need() is not None:
+            needs.append(self.embedder.cache_need())
         return needs
 
     # ---------------------------------------------------------------- one step
@@ -174,7 +197,9 @@ class DecoderModel:
         b, ops = ctx.batch, ctx.ops
         ctx.defer_ok = self._norms_accept_deferred and getattr(ops, "deferred", False)
         ctx.hints_ok = getattr(ops, "takes_hints", False)
-        if self.embedding_norm is not None:                    # gather and norm in one kernel; the stream starts normed
+        if self.embedder is not None:                          # its cache entry, if it keeps state, lies behind the steps'
+            x = self.embedder.forward(b.token_ids, self.embedding, ctx, caches[len(self.spec.order)] if len(caches) > len(self.spec.order) else None)
+        elif self.embedding_norm is not None:                  # gather and norm in one kernel; the stream starts normed
             x = self.embedding_norm.embed(b.token_ids, self.embedding, ctx, float32=self.spec.residual == "float32")
         elif self.spec.residual == "float32":                  # the stream in float32 and, beside it, its rows in the run's dtype
             x, rows = ops.embed_stream(b.token_ids, self.embedding, ctx.dtype)
@@ -195,4 +220,7 @@ class DecoderModel:
         if b.num_logit_rows == 0:
             return None
         h = self.final_norm.forward(x, delta, ctx, rows=b.logit_rows)
-        return ops.linear(h, self.lm_head, out_dtype=torch.float32)
+        logits = ops.linear(h, self.lm_head, out_dtype=torch.float32)
+        if self.spec.logit_softcap is not None:
+            logits = ops.softcap(logits, float(self.spec.logit_softcap))
+        return logits

@@ -59,8 +59,9 @@ class ScalarRMSNorm(Part):
 @register_norm("stream_rmsnorm")
 class StreamRMSNorm(Part):
     """y = w * x / sqrt(mean(x^2) + eps) on a float32 residual stream, rows handed out in the run's dtype
-    (a pending delta, if any, is added to the stream first, in float32)."""
+    (a pending delta, if any, is added to the stream first, in float32; a GatedDelta is gated in the same kernel)."""
     keeps_float32_stream = True
+    takes_gated_delta = True
 
     def __init__(self, spec):
         super().__init__(spec)

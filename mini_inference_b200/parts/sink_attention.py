@@ -9,12 +9,19 @@
   value_mix    "source": this layer's values are left in the step context for later layers;
                "blend": v <- (1 - lambda) v + lambda v_source with lambda the tensor `vmix` and v_source the source
                layer's values of the same tokens; the blended v is what is cached
+               sink="learned": the term is exp(sink_h) with one learned number per head (the tensor `sink`) instead of 1
+  distance_bias  (rows, far): a learned table `rel` [rows, heads] is added to the scaled scores by the distance n = i - j >= 0:
+               row n for n < rows / 2, else min(rows - 1, rows/2 + floor(ln(n / (rows/2)) / ln(far / (rows/2)) * (rows - rows/2)))
+               (one row per distance near by, logarithmic steps that reach the last row at `far`).  The table is spread out
+               once, when the weights are loaded, into one float32 row per distance 0 .. far, which the kernels index directly
   key and value rows may differ in size (key_dim, value_dim); the value pool is then a tensor of its own.
 
 q, k, v come from one product; one kernel norms q and k, blends v and writes k and v into the step's pages
 before attention runs, so a portion attends to itself through the cache.  Scores, softmax weights and the weighted
 sum are float32."""
 from __future__ import annotations
+
+import math
 
 import torch
 
@@ -33,13 +40,18 @@ class SinkAttention(Part):
         self.D, self.V, self.scale = int(g("key_dim")), int(g("value_dim")), float(g("scale"))
         self.eps = g("unit_norm_eps")                       # None: q and k are used as projected
         self.block_size, self.window, self.sink = g("block_size"), g("window"), bool(g("sink", False))
+        self.learned_sink = g("sink", False) == "learned"
+        self.distance_bias = tuple(g("distance_bias")) if g("distance_bias") else None          # (rows, far)
+        # rows = -1: the checkpoint's table says how many rows there are
+        if self.distance_bias and self.distance_bias[0] >= 0 and not 0 < self.distance_bias[0] // 2 < self.distance_bias[1]:
+            raise ValueError("distance_bias needs at least two rows and a far distance beyond half of them")
         self.value_mix = g("value_mix")
         self.mix_key = g("value_mix_key", "values")
         if self.H % self.KV:
             raise ValueError(f"{self.H} query heads are not a multiple of {self.KV} kv heads")
         if self.value_mix not in (None, "source", "blend"):
             raise ValueError(f"value_mix '{self.value_mix}' is not one of source, blend")
-        self.qkv = self.o = self.lam = None
+        self.qkv = self.o = self.lam = self.sink_values = self.bias_by_distance = None
 
     def weight_specs(self):
         H, KV, D, V, hid = self.H, self.KV, self.D, self.V, self.hidden
@@ -47,7 +59,18 @@ class SinkAttention(Part):
                  WeightSpec("o", (hid, H * V))]
         if self.value_mix:                                  # a source layer's checkpoint holds the number too; it is not used
             specs.append(WeightSpec("vmix", (), kind="vector", init="norm"))
+        if self.learned_sink:
+            specs.append(WeightSpec("sink", (H,), kind="vector"))
+        if self.distance_bias:
+            specs.append(WeightSpec("rel", (self.distance_bias[0], H), kind="vector"))
         return specs
+
+    @staticmethod
+    def distance_row(n: int, rows: int, far: int) -> int:
+        half = rows // 2
+        if n < half:
+            return n
+        return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
 
     def cache_need(self):
         return KVCacheNeed(self.KV, self.D, self.window, value_dim=None if self.V == self.D else self.V)
@@ -57,6 +80,14 @@ class SinkAttention(Part):
         self.o = tensors.pop("o")
         if self.value_mix == "blend":
             self.lam = tensors["vmix"].float().reshape(1).contiguous()
+        if self.learned_sink:
+            self.sink_values = tensors["sink"].float().contiguous()
+        if self.distance_bias:
+            rows, far = tensors["rel"].shape[0], int(self.distance_bias[1])
+            if not 0 < rows // 2 < far:
+                raise ValueError("distance_bias needs at least two rows and a far distance beyond half of them")
+            index = torch.tensor([self.distance_row(n, rows, far) for n in range(far + 1)], dtype=torch.long, device=device)
+            self.bias_by_distance = tensors["rel"].float()[index].contiguous()          # [far + 1, H]; distances beyond far read the last row
 
     step_arrays = staticmethod(paged_attention_step_arrays)
 
@@ -80,5 +111,9 @@ class SinkAttention(Part):
             ctx.shared[("value_mix", self.mix_key)] = p[:, (H + KV) * D:]      # a view: the kernel below leaves these columns alone
         q = ops.unit_qk_cache(p, H, KV, D, V, self.eps, self.lam, source, meta,
                               cache.k if owns_cache else None, cache.v if owns_cache else None)
-        o = ops.masked_attention(q, cache.k, cache.v, meta, H, KV, D, V, self.scale, self.block_size, self.window, self.sink)
+        if self.learned_sink or self.distance_bias:
+            o = ops.masked_attention(q, cache.k, cache.v, meta, H, KV, D, V, self.scale, self.block_size, self.window, self.sink,
+                                     sink_values=self.sink_values, distance_bias=self.bias_by_distance)
+        else:
+            o = ops.masked_attention(q, cache.k, cache.v, meta, H, KV, D, V, self.scale, self.block_size, self.window, self.sink)
         return ops.linear(o, self.o)

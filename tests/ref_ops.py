@@ -310,7 +310,8 @@ def _unit_qk_cache(self, p, H, KV, D, V, eps, lam, source, meta, k_cache, v_cach
         q, k = _rms(q, eps), _rms(k, eps)
     if source is not None:
         v = (1.0 - lam.float()) * v + lam.float() * source.float().view(T, KV, V)
-    p[:, :H * D] = q.reshape(T, H * D).to(dt)
+    if eps is not None:
+        p[:, :H * D] = q.reshape(T, H * D).to(dt)
     if k_cache is not None:
         page, off = meta.slots.long() // meta.page_size, meta.slots.long() % meta.page_size
         k_cache[page, :, off, :] = k.to(dt)
@@ -405,9 +406,224 @@ def _expert_ffn(self, h, chosen, weights, w_in, w_out, limit, slope, shared):
     return acc.to(h.dtype)
 
 
+# ---------------------------------------------------------------- hashed pair embedding, filters, gated additions, three more recurrences
+def _embed_bigram_stream(self, ids, table, pairs, buckets, mul_prev, mul_cur, state, batch):
+    ids_l, pos = ids.long(), batch.positions.long()
+    prev = torch.roll(ids_l, 1)
+    for a, b, slot in _segments(batch):
+        prev[a] = state[slot, 0].long()
+        state[slot, 0] = ids[b - 1]
+    row = (prev * mul_prev + ids_l * mul_cur) % buckets
+    row = torch.where(pos == 0, torch.full_like(row, buckets), row)
+    return table[ids_l].float() + pairs[row].float()
+
+
+_plain_stream_rmsnorm = _stream_rmsnorm
+
+
+def _stream_rmsnorm_gated(self, x, delta, weight, eps, rows, out_dtype):
+    from mini_inference_b200.parts.base import GatedDelta
+    if isinstance(delta, GatedDelta):
+        y = delta.y.float() if delta.y_bias is None else delta.y.float() + delta.y_bias.float()
+        delta = torch.sigmoid(delta.logits.float() + delta.bias.float()) * y
+    return _plain_stream_rmsnorm(self, x, delta, weight, eps, rows, out_dtype)
+
+
+def _short_conv(self, h, weight, bias, taps, state, offset, batch, residual=False, act="none"):
+    T, C = h.shape
+    out = torch.empty(T, C, dtype=torch.float32, device=h.device)
+    x = h.float()
+    for a, b, slot in _segments(batch):
+        hist = state[slot, offset:offset + (taps - 1) * C].view(taps - 1, C) if taps > 1 else x[:0]
+        ext = torch.cat([hist, x[a:b]], dim=0)
+        y = torch.zeros(b - a, C, device=h.device)
+        for j in range(taps):
+            y += weight[:, j].float() * ext[j:j + b - a]
+        if bias is not None:
+            y = y + bias.float()
+        if act == "silu":
+            y = torch.nn.functional.silu(y)
+        out[a:b] = y + x[a:b] if residual else y
+        if taps > 1:
+            state[slot, offset:offset + (taps - 1) * C] = ext[ext.shape[0] - (taps - 1):].reshape(-1)
+    return out.to(h.dtype)
+
+
+def _general_delta_prepare(self, p, w2, w0, a_b, H, D, V, rank, decay_scale, unit_eps):
+    T, HD = p.shape[0], H * D
+    f = p.float()
+    r, k, v = f[:, :HD], f[:, HD:2 * HD], f[:, 2 * HD:2 * HD + H * V]
+    a = torch.sigmoid(f[:, 2 * HD + H * V:3 * HD + H * V] + a_b.float())
+    low = torch.tanh(f[:, 3 * HD + 2 * H * V:3 * HD + 2 * H * V + rank])
+    d = torch.exp(-decay_scale * torch.sigmoid(low @ w2.float().T + w0.float()))
+    kh = k.view(T, H, D)
+    u = (kh / torch.sqrt(kh.pow(2).sum(-1, keepdim=True) + unit_eps)).reshape(T, HD)
+    return torch.cat([r, k, u, a * u, d, v], dim=1).contiguous()                   # r | k | u | a u | decay | v
+
+
+def _general_delta_scan(self, prep, H, D, V, state, batch):
+    T, HD = prep.shape[0], H * D
+    r, k, u, au, d = (prep[:, i * HD:(i + 1) * HD].view(T, H, D) for i in range(5))
+    v = prep[:, 5 * HD:5 * HD + H * V].view(T, H, V)
+    o = torch.zeros(T, H * V, dtype=torch.float32, device=prep.device)
+    for a, b, slot in _segments(batch):
+        S = state[slot, :HD * V].view(H, D, V).clone()
+        for t in range(a, b):
+            seen = torch.einsum("hd,hdv->hv", u[t], S)
+            S = d[t][:, :, None] * S - au[t][:, :, None] * seen[:, None, :] + k[t][:, :, None] * v[t][:, None, :]
+            o[t] = torch.einsum("hdv,hd->hv", S, r[t]).reshape(-1)
+        state[slot, :HD * V] = S.reshape(-1)
+    return o
+
+
+def _matrix_memory(self, p, gl, gate_bias, H, D, V, cap, den_eps, norm, gate, eps, state, batch, out_dtype):
+    T, HD, W = p.shape[0], H * D, V + 4
+    f = p.float()
+    q = f[:, :HD].view(T, H, D) * D ** -0.5
+    k = f[:, HD:2 * HD].view(T, H, D)
+    v = f[:, 2 * HD:2 * HD + H * V].view(T, H, V)
+    z = gl.float() + gate_bias.float()
+    if cap is not None:
+        z = cap * torch.tanh(z / cap)
+    ig, fg = z[:, :H], torch.nn.functional.logsigmoid(z[:, H:])
+    o = torch.zeros(T, H, V, dtype=torch.float32, device=p.device)
+    for a, b, slot in _segments(batch):
+        S = state[slot, :HD * W].view(H, D, W).clone()                 # columns 0..V-1 the memory, column V the normaliser
+        m = state[slot, HD * W:HD * W + H].clone()
+        for t in range(a, b):
+            new = torch.maximum(fg[t] + m, ig[t])
+            keep, take = torch.exp(fg[t] + m - new), torch.exp(ig[t] - new)
+            vv = torch.cat([v[t], torch.ones(H, 1), torch.zeros(H, 3)], dim=1)
+            S = keep[:, None, None] * S + (take[:, None] * k[t])[:, :, None] * vv[:, None, :]
+            m = new
+            full = torch.einsum("hdw,hd->hw", S, q[t])
+            den = torch.maximum(full[:, V].abs(), torch.exp(-m)) + den_eps
+            o[t] = full[:, :V] / den[:, None]
+        state[slot, :HD * W] = S.reshape(-1)
+        state[slot, HD * W:HD * W + H] = m
+    y = _rms(o, eps).reshape(T, H * V) * norm.float() * torch.sigmoid(gate.float())
+    return y.to(out_dtype)
+
+
+def _selective_scan(self, x, dt, dt_b, A, B, C, Dv, z, state, batch, out_dtype):
+    T, I = x.shape
+    N = A.shape[1]
+    xf, zf, Bf, Cf = x.float(), z.float(), B.float(), C.float()
+    step = torch.nn.functional.softplus(dt.float() + dt_b.float())
+    y = torch.zeros(T, I, dtype=torch.float32, device=x.device)
+    for a, b, slot in _segments(batch):
+        S = state[slot, :I * N].view(I, N).clone()
+        for t in range(a, b):
+            S = torch.exp(step[t][:, None] * A) * S + (step[t] * xf[t])[:, None] * Bf[t][None, :]
+            y[t] = S @ Cf[t] + Dv.float() * xf[t]
+        state[slot, :I * N] = S.reshape(-1)
+    return (y * torch.nn.functional.silu(zf)).to(out_dtype)
+
+
+_plain_masked_attention = _masked_attention
+
+
+def _masked_attention_biased(self, q, k_cache, v_cache, meta, H, KV, D, V, scale, block_size, window, sink, sink_values=None,
+                             distance_bias=None):
+    if sink_values is None and distance_bias is None:
+        return _plain_masked_attention(self, q, k_cache, v_cache, meta, H, KV, D, V, scale, block_size, window, sink)
+    T = q.shape[0]
+    out = torch.empty((T, H * V), dtype=q.dtype, device=q.device)
+    q_start, pos0, kv_len = meta.seg_q_start.tolist(), meta.seg_pos0.tolist(), meta.seg_kv_len.tolist()
+    ps = meta.page_size
+    rows = getattr(meta, "table_rows", None)
+    rows = list(range(len(pos0))) if rows is None else rows.tolist()
+    for s in range(len(pos0)):
+        a, b, L = q_start[s], q_start[s + 1], kv_len[s]
+        j = torch.arange(L, device=q.device)
+        pages = meta.block_table[rows[s], j // ps].long()
+        k = k_cache[pages, :, j % ps, :].float().repeat_interleave(H // KV, dim=1)
+        v = v_cache[pages, :, j % ps, :].float().repeat_interleave(H // KV, dim=1)
+        p = pos0[s] + torch.arange(b - a, device=q.device)
+        dist = p[:, None] - j[None, :]
+        visible = dist >= 0
+        if window is not None:
+            visible &= dist < window
+        if block_size is not None:
+            visible &= (j[None, :] // block_size) == (p[:, None] // block_size)
+        sc = torch.einsum("phd,jhd->hpj", q[a:b].reshape(b - a, H, D).float(), k) * scale
+        if distance_bias is not None:
+            sc = sc + distance_bias[dist.clamp(0, distance_bias.shape[0] - 1)].permute(2, 0, 1)
+        sc = sc.masked_fill(~visible[None], float("-inf"))
+        m = sc.max(-1, keepdim=True).values
+        extra = 0.0
+        if sink:
+            sv = sink_values.float().view(H, 1, 1) if sink_values is not None else torch.zeros(H, 1, 1)
+            m = torch.maximum(m, sv)
+            extra = torch.exp(sv - m)
+        e = torch.exp(sc - m)
+        out[a:b] = torch.einsum("hpj,jhd->phd", e / (e.sum(-1, keepdim=True) + extra), v).reshape(b - a, H * V).to(q.dtype)
+    return out
+
+
+def _dual_rmsnorm_mix(self, a, wa, sa, b, wb, sb, eps):
+    return (sa * _rms(a.float(), eps) * wa.float() + sb * _rms(b.float(), eps) * wb.float()).to(a.dtype)
+
+
+_plain_route_topk = _route_topk
+
+
+def _route_topk_scored(self, h, router, correction, top, groups, score="softmax", extra_rows=0):
+    if score == "softmax" and not extra_rows:
+        return _plain_route_topk(self, h, router, correction, top, groups)
+    E = router.shape[0] - extra_rows
+    logits = h.float() @ router.float().T
+    extra = logits[:, E:].contiguous() if extra_rows else None
+    s = torch.sigmoid(logits[:, :E]) if score == "sigmoid" else torch.softmax(logits[:, :E], dim=-1)
+    choice = s if correction is None else s + correction.float()
+    assert not groups
+    idx = torch.sort(choice, dim=-1, descending=True, stable=True).indices[:, :top]
+    return idx.to(torch.int32), s.gather(1, idx), extra
+
+
+_plain_expert_ffn = _expert_ffn
+
+
+def _expert_ffn_general(self, h, chosen, weights, w_in, w_out, limit, slope, shared, up_shift=1.0, weight_on_input=False, shared_gate=None):
+    if up_shift == 1.0 and not weight_on_input and shared_gate is None:
+        return _plain_expert_ffn(self, h, chosen, weights, w_in, w_out, limit, slope, shared)
+    T, top = chosen.shape
+    acc = torch.zeros(T, w_out.shape[1], dtype=torch.float32, device=h.device)
+    for j in range(top):
+        for e in chosen[:, j].unique().tolist():
+            rows = (chosen[:, j] == e).nonzero().flatten()
+            w = weights[rows, j:j + 1].float()
+            g, u = (h[rows].float() @ w_in[e].float().T).chunk(2, dim=-1)
+            if weight_on_input:
+                g, u = g * w, u * w
+            g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+            act = (g * torch.sigmoid(slope * g) * (u + up_shift)).to(h.dtype)
+            y = self.linear(act, w_out[e]).float()
+            acc[rows] += y if weight_on_input else w * y
+    if shared is not None:
+        acc += shared.float() if shared_gate is None else torch.sigmoid(shared_gate.float()) * shared.float()
+    return acc.to(h.dtype)
+
+
+def _bias_act(self, z, bias, act):
+    y = z.float() + bias.float()
+    if act == "relu2":
+        y = torch.relu(y).pow(2)
+    return y.to(z.dtype)
+
+
+def _softcap(self, logits, cap):
+    return cap * torch.tanh(logits / cap)
+
+
+_stream_rmsnorm, _masked_attention, _route_topk, _expert_ffn = _stream_rmsnorm_gated, _masked_attention_biased, _route_topk_scored, _expert_ffn_general
+
+
 for _name, _fn in list(globals().items()):
     if _name.startswith("_") and _name[1:] in ("embed_scaled_norm", "add_scaled_rmsnorm", "polynorm", "lightning_scan", "group_rmsnorm_gate",
                                                "delta_prepare", "delta_scan", "batched_linear", "latent_prepare", "latent_attention", "head_gate",
                                                "embed_stream", "cast_rows", "out_rmsnorm_add", "stream_rmsnorm", "unit_qk_cache", "masked_attention",
-                                               "retention_scan", "route_topk", "clamped_glu", "expert_ffn"):
+                                               "retention_scan", "route_topk", "clamped_glu", "expert_ffn",
+                                               "embed_bigram_stream", "short_conv", "general_delta_prepare", "general_delta_scan", "matrix_memory",
+                                               "selective_scan", "dual_rmsnorm_mix", "bias_act", "softcap"):
         setattr(TorchRefOps, _name[1:], _fn)
