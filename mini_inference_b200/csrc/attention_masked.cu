@@ -4,6 +4,9 @@
 //             (blocks counted from position 0 of the sequence); with window > 0 only the last `window`
 //   sink      one more softmax term whose score is 0 and which carries no value: p_j = exp(s_j) / (1 + sum exp(s_j));
 //             a running maximum that starts at 0 with a running sum that starts at 1 is exactly that
+//             sink_values: the term is exp(sink_values[h]) instead (a learned score per head; it is not scaled and gets no bias)
+//   bias      a float32 table [bias_last + 1, H] added to the scaled score by the distance i - j (distances beyond bias_last
+//             read the last row)
 //   sizes     key rows of D and value rows of Dv entries (up to 256; any size, 16-byte loads where rows allow), each in a pool of its own:
 //             k_cache [pages, KV, page_size, D], v_cache [pages, KV, page_size, Dv]
 //
@@ -27,7 +30,8 @@ constexpr int WARPS = 4;
 template <typename T>
 __device__ __forceinline__ void attend_keys(const float* q_s, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                                             const int* __restrict__ table_row, int kvh, int KV, int D, int Dv, int ps,
-                                            int lo, int hi, float& m, float& l, float (&acc)[MAX_D / 32]) {
+                                            int lo, int hi, float& m, float& l, float (&acc)[MAX_D / 32],
+                                            const float* __restrict__ bias = nullptr, int bias_last = 0, int H = 0, int h = 0, int qpos = 0) {
     const int lane = threadIdx.x & 31;
     constexpr int VN = Vec16<T>::N;
     for (int j0 = lo; j0 < hi; j0 += 32) {
@@ -48,7 +52,7 @@ __device__ __forceinline__ void attend_keys(const float* q_s, const T* __restric
             } else {
                 for (int c = 0; c < D; ++c) dot += q_s[c] * to_f32(kr[c]);
             }
-            s = dot;
+            s = bias ? dot + bias[(size_t)min(qpos - j, bias_last) * H + h] : dot;
         }
         const float m_new = fmaxf(m, warp_max(s));
         const float alpha = expf(m - m_new);              // nothing seen yet and no sink: exp(-inf) = 0
@@ -83,7 +87,8 @@ __global__ void masked_prefill_kernel(const T* __restrict__ q, int q_stride, con
                                       T* __restrict__ out, const int* __restrict__ tiles, const int* __restrict__ seg_q_start,
                                       const int* __restrict__ seg_pos0, const int* __restrict__ block_table,
                                       const int* __restrict__ table_rows, int table_stride, int H, int KV, int D, int Dv, int ps,
-                                      int tile_rows, float scale, int block, int window, int sink) {
+                                      int tile_rows, float scale, int block, int window, int sink,
+                                      const float* __restrict__ sink_values, const float* __restrict__ bias, int bias_last) {
     __shared__ float q_s[WARPS][MAX_D];
     const int seg = tiles[2 * blockIdx.x], r0 = tiles[2 * blockIdx.x + 1];
     const int h = blockIdx.y, kvh = h / (H / KV);
@@ -96,10 +101,11 @@ __global__ void masked_prefill_kernel(const T* __restrict__ q, int q_stride, con
         const T* qr = q + (size_t)tok * q_stride + (size_t)h * D;
         for (int d = lane; d < D; d += 32) q_s[warp][d] = to_f32(qr[d]) * scale;
         __syncwarp();
-        float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f, acc[MAX_D / 32];
+        float m = sink ? (sink_values ? sink_values[h] : 0.f) : -INFINITY, l = sink ? 1.f : 0.f, acc[MAX_D / 32];
 #pragma unroll
         for (int k = 0; k < MAX_D / 32; ++k) acc[k] = 0.f;
-        attend_keys<T>(q_s[warp], k_cache, v_cache, table_row, kvh, KV, D, Dv, ps, first_key(p, block, window), p + 1, m, l, acc);
+        attend_keys<T>(q_s[warp], k_cache, v_cache, table_row, kvh, KV, D, Dv, ps, first_key(p, block, window), p + 1, m, l, acc,
+                       bias, bias_last, H, h, p);
         T* orow = out + ((size_t)tok * H + h) * Dv;
 #pragma unroll
         for (int k = 0; k < MAX_D / 32; ++k) {
@@ -118,7 +124,8 @@ __global__ void masked_decode_kernel(const T* __restrict__ q, int q_stride, cons
                                      const int* __restrict__ decode_segs, const int* __restrict__ seg_q_start,
                                      const int* __restrict__ seg_kv_len, const int* __restrict__ block_table,
                                      const int* __restrict__ table_rows, int table_stride, int H, int KV, int D, int Dv, int ps,
-                                     float scale, int block, int window, int sink) {
+                                     float scale, int block, int window, int sink,
+                                     const float* __restrict__ sink_values, const float* __restrict__ bias, int bias_last) {
     __shared__ float q_s[WARPS][MAX_D];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int h = blockIdx.y * WARPS + warp;
@@ -134,12 +141,12 @@ __global__ void masked_decode_kernel(const T* __restrict__ q, int q_stride, cons
     for (int d = lane; d < D; d += 32) q_s[warp][d] = to_f32(qr[d]) * scale;
     __syncwarp();
     const bool own_sink = sink && S == 1;
-    float m = own_sink ? 0.f : -INFINITY, l = own_sink ? 1.f : 0.f, acc[MAX_D / 32];
+    float m = own_sink ? (sink_values ? sink_values[h] : 0.f) : -INFINITY, l = own_sink ? 1.f : 0.f, acc[MAX_D / 32];
 #pragma unroll
     for (int k = 0; k < MAX_D / 32; ++k) acc[k] = 0.f;
     if (lo < hi)
         attend_keys<T>(q_s[warp], k_cache, v_cache, block_table + (size_t)(table_rows ? table_rows[seg] : seg) * table_stride, kvh, KV,
-                       D, Dv, ps, lo, hi, m, l, acc);
+                       D, Dv, ps, lo, hi, m, l, acc, bias, bias_last, H, h, len - 1);
     const float inv = l > 0.f ? 1.f / l : 0.f;                  // empty piece: output 0, lse -inf
     if (S == 1) {
         T* orow = out + ((size_t)tok * H + h) * Dv;
@@ -154,16 +161,18 @@ __global__ void masked_decode_kernel(const T* __restrict__ q, int q_stride, cons
     }
 }
 
-// out = sum_s e^(lse_s - mx) o_s / (sum_s e^(lse_s - mx) + [sink] e^(-mx)),  mx = max(lse_s, [sink] 0)
+// out = sum_s e^(lse_s - mx) o_s / (sum_s e^(lse_s - mx) + [sink] e^(sv - mx)),  mx = max(lse_s, [sink] sv),  sv the sink's score (0 or learned)
 template <typename T>
 __global__ void masked_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ lse_part, T* __restrict__ out,
-                                    const int* __restrict__ decode_segs, const int* __restrict__ seg_q_start, int H, int Dv, int S, int sink) {
+                                    const int* __restrict__ decode_segs, const int* __restrict__ seg_q_start, int H, int Dv, int S, int sink,
+                                    const float* __restrict__ sink_values) {
     const int i = blockIdx.x, h = blockIdx.y;
+    const float sv = sink_values ? sink_values[h] : 0.f;
     const int tok = seg_q_start[decode_segs[i]];
     const size_t base = ((size_t)i * H + h) * S;
-    float mx = sink ? 0.f : -INFINITY;
+    float mx = sink ? sv : -INFINITY;
     for (int s = 0; s < S; ++s) mx = fmaxf(mx, lse_part[base + s]);
-    float den = sink ? expf(-mx) : 0.f;
+    float den = sink ? expf(sv - mx) : 0.f;
     for (int s = 0; s < S; ++s) den += expf(lse_part[base + s] - mx);
     for (int d = threadIdx.x; d < Dv; d += blockDim.x) {
         float num = 0.f;
@@ -226,12 +235,13 @@ MI_EXPORT int mi_unit_qk_cache(void* p, int ldp, const void* v_src, int ld_src, 
 MI_EXPORT int mi_masked_prefill(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out, const int* tiles,
                                 int num_tiles, const int* seg_q_start, const int* seg_pos0, const int* block_table,
                                 const int* table_rows, int table_stride, int H, int KV, int D, int Dv, int ps, int tile_rows, float scale,
-                                int block, int window, int sink, int dtype, cudaStream_t stream) {
+                                int block, int window, int sink, const float* sink_values, const float* bias, int bias_last, int dtype,
+                                cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     if (D > MAX_D || Dv > MAX_D || H > 65535) return -2;
     dim3 grid(num_tiles, H);
 #define ARGS(T) (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, (T*)out, tiles, seg_q_start, seg_pos0, block_table, table_rows, \
-        table_stride, H, KV, D, Dv, ps, tile_rows, scale, block, window, sink
+        table_stride, H, KV, D, Dv, ps, tile_rows, scale, block, window, sink, sink_values, bias, bias_last
     if (dtype == MI_BF16) masked_prefill_kernel<__nv_bfloat16><<<grid, WARPS * 32, 0, stream>>>(ARGS(__nv_bfloat16));
     else masked_prefill_kernel<float><<<grid, WARPS * 32, 0, stream>>>(ARGS(float));
 #undef ARGS
@@ -241,12 +251,13 @@ MI_EXPORT int mi_masked_prefill(const void* q, int q_stride, const void* k_cache
 MI_EXPORT int mi_masked_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out, float* o_part,
                                float* lse_part, const int* decode_segs, int num_decode, const int* seg_q_start, const int* seg_kv_len,
                                const int* block_table, const int* table_rows, int table_stride, int H, int KV, int D, int Dv, int ps,
-                               int splits, float scale, int block, int window, int sink, int dtype, cudaStream_t stream) {
+                               int splits, float scale, int block, int window, int sink, const float* sink_values, const float* bias,
+                               int bias_last, int dtype, cudaStream_t stream) {
     if (num_decode == 0) return 0;
     if (D > MAX_D || Dv > MAX_D || H > 65535 * WARPS) return -2;
     dim3 grid(num_decode, (H + WARPS - 1) / WARPS, splits);
 #define ARGS(T) (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, (T*)out, o_part, lse_part, decode_segs, seg_q_start, seg_kv_len, \
-        block_table, table_rows, table_stride, H, KV, D, Dv, ps, scale, block, window, sink
+        block_table, table_rows, table_stride, H, KV, D, Dv, ps, scale, block, window, sink, sink_values, bias, bias_last
     if (dtype == MI_BF16) masked_decode_kernel<__nv_bfloat16><<<grid, WARPS * 32, 0, stream>>>(ARGS(__nv_bfloat16));
     else masked_decode_kernel<float><<<grid, WARPS * 32, 0, stream>>>(ARGS(float));
 #undef ARGS
@@ -254,8 +265,8 @@ MI_EXPORT int mi_masked_decode(const void* q, int q_stride, const void* k_cache,
     if (err || splits == 1) return err;
     dim3 mgrid(num_decode, H);
     if (dtype == MI_BF16)
-        masked_merge_kernel<__nv_bfloat16><<<mgrid, 128, 0, stream>>>(o_part, lse_part, (__nv_bfloat16*)out, decode_segs, seg_q_start, H, Dv, splits, sink);
+        masked_merge_kernel<__nv_bfloat16><<<mgrid, 128, 0, stream>>>(o_part, lse_part, (__nv_bfloat16*)out, decode_segs, seg_q_start, H, Dv, splits, sink, sink_values);
     else
-        masked_merge_kernel<float><<<mgrid, 128, 0, stream>>>(o_part, lse_part, (float*)out, decode_segs, seg_q_start, H, Dv, splits, sink);
+        masked_merge_kernel<float><<<mgrid, 128, 0, stream>>>(o_part, lse_part, (float*)out, decode_segs, seg_q_start, H, Dv, splits, sink, sink_values);
     return (int)cudaGetLastError();
 }

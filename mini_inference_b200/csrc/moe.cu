@@ -5,12 +5,17 @@
 //                choice scores c = s + correction; with groups, only experts of the `keep` groups (equal groups of
 //                neighbouring experts) whose largest c is largest stay eligible (the others count as -inf); the `top`
 //                largest c are chosen (ties: the lower index); the weights are the chosen experts' s, as they are.
+//                Options: s = sigmoid(logit) per expert instead of the softmax; no correction; `extra` further rows behind the
+//                experts' rows of the router matrix whose float32 logits are handed out as they are (a gate that reads the
+//                same input rides along in the router's pass).
+//   scale rows   a design whose scores multiply the experts' INPUTS: row p = weight[p] * h[p / top] per pair, rounded to the
+//                run's dtype; the products then run with one choice per row and the sum adds the rows unweighted.
 //   align        pairs p = token * top + j counted per expert; every expert's rows start on a multiple of the row tile
 //                (padding rows are marked -1), so a tile of rows belongs to ONE expert: tile_expert[tile] (-1 past the end).
 //                Nothing returns to the host: the grids of the products cover the most tiles there can be, and a block
 //                whose tile has no expert leaves at once.
 //   grouped in   rows gathered by token; per expert [gate rows | up rows]; the epilogue applies
-//                g = min(gate, limit), u = clamp(up, -limit, limit), y = g * sigmoid(slope * g) * (u + 1).
+//                g = min(gate, limit), u = clamp(up, -limit, limit), y = g * sigmoid(slope * g) * (u + shift)  (shift 1 with finite limits; shift 0, slope 1 and no limit: silu(gate) * up).
 //   grouped out  y rows times the expert's down matrix, written to the pair's own row (so the order of pairs inside an
 //                expert's segment, which comes from atomics, does not reach the result).
 //   combine      out[t] = sum_j weight[t, j] * row[t * top + j] (+ the shared expert's row), float32, in the order of choice.
@@ -39,13 +44,17 @@ __device__ __forceinline__ void warp_best(float& bv, int& bi) {
 
 // One warp makes one token's choice from its logits s[E] (left as softmax scores); c and gb are scratch of E floats each.
 __device__ __forceinline__ void warp_choose(float* s, float* c, float* gb, const float* __restrict__ corr, int E, int top, int g_count,
-                                            int g_keep, int* __restrict__ chosen, float* __restrict__ weights, int lane) {
-    float mx = -INFINITY, den = 0.f;
-    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
-    mx = warp_max(mx);
-    for (int e = lane; e < E; e += 32) { const float v = expf(s[e] - mx); s[e] = v; den += v; }
-    den = warp_sum(den);
-    for (int e = lane; e < E; e += 32) { s[e] = s[e] / den; c[e] = s[e] + corr[e]; }
+                                            int g_keep, int* __restrict__ chosen, float* __restrict__ weights, int lane, int sigmoid_scores) {
+    if (sigmoid_scores) {
+        for (int e = lane; e < E; e += 32) { s[e] = 1.f / (1.f + expf(-s[e])); c[e] = corr ? s[e] + corr[e] : s[e]; }
+    } else {
+        float mx = -INFINITY, den = 0.f;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
+        mx = warp_max(mx);
+        for (int e = lane; e < E; e += 32) { const float v = expf(s[e] - mx); s[e] = v; den += v; }
+        den = warp_sum(den);
+        for (int e = lane; e < E; e += 32) { s[e] = s[e] / den; c[e] = corr ? s[e] + corr[e] : s[e]; }
+    }
     __syncwarp();
     if (g_count > 0) {
         const int per = E / g_count;
@@ -90,10 +99,11 @@ __device__ __forceinline__ void warp_choose(float* s, float* c, float* gb, const
 template <typename T, int TOK>
 __global__ void __launch_bounds__(TOK == 1 ? 1024 : 256) route_topk_kernel(const T* __restrict__ h, int ldh, const T* __restrict__ router, const float* __restrict__ corr,
                                                          int* __restrict__ chosen, float* __restrict__ weights, int T_, int hidden, int E, int top,
-                                                         int g_count, int g_keep) {
+                                                         int g_count, int g_keep, int sigmoid_scores, int extra, float* __restrict__ extra_out) {
     extern __shared__ __align__(16) float rsm[];
+    const int EA = E + extra;                          // rows of the router matrix: the experts', then the extra ones
     float* hs = rsm;                                   // [TOK][hidden]
-    float* sc = hs + (size_t)TOK * hidden;             // [TOK][3][E]: scores, choice scores, group scratch
+    float* sc = hs + (size_t)TOK * hidden;             // [TOK][3][EA]: logits -> scores, choice scores, group scratch
     const int t0 = blockIdx.x * TOK, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const int nt = min(TOK, T_ - t0);
     for (int i = threadIdx.x; i < TOK * hidden; i += blockDim.x) {
@@ -102,7 +112,7 @@ __global__ void __launch_bounds__(TOK == 1 ? 1024 : 256) route_topk_kernel(const
     }
     __syncthreads();
     const bool vec = hidden % 4 == 0 && ((uintptr_t)router % 16) == 0;
-    for (int e = warp; e < E; e += nw) {
+    for (int e = warp; e < EA; e += nw) {
         const T* w = router + (size_t)e * hidden;
         float dot[TOK];
 #pragma unroll
@@ -130,26 +140,27 @@ __global__ void __launch_bounds__(TOK == 1 ? 1024 : 256) route_topk_kernel(const
 #pragma unroll
         for (int k = 0; k < TOK; ++k) {
             const float d = warp_sum(dot[k]);
-            if (lane == 0) sc[(size_t)k * 3 * E + e] = d;
+            if (lane == 0) sc[(size_t)k * 3 * EA + e] = d;
         }
     }
     __syncthreads();
     for (int tk = warp; tk < nt; tk += nw) {
-        float* s = sc + (size_t)tk * 3 * E;
+        float* s = sc + (size_t)tk * 3 * EA;
         const size_t t = t0 + tk;
-        warp_choose(s, s + E, s + 2 * E, corr, E, top, g_count, g_keep, chosen + t * top, weights + t * top, lane);
+        for (int r = lane; r < extra; r += 32) extra_out[t * extra + r] = s[E + r];
+        warp_choose(s, s + EA, s + 2 * EA, corr, E, top, g_count, g_keep, chosen + t * top, weights + t * top, lane, sigmoid_scores);
     }
 }
 
 // ------------------------------------------------------------------ g = min(gate, limit); u = clamp(up); g sigmoid(slope g) (u + 1)
-__device__ __forceinline__ float clamped_glu(float g, float u, float limit, float slope) {
+__device__ __forceinline__ float clamped_glu(float g, float u, float limit, float slope, float shift) {
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
-    return g / (1.f + expf(-slope * g)) * (u + 1.f);
+    return g / (1.f + expf(-slope * g)) * (u + shift);
 }
 
 template <typename T>
-__global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, float limit, float slope, int vec) {
+__global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, float limit, float slope, float shift, int vec) {
     const T* row = gu + (size_t)blockIdx.x * 2 * inter;
     T* o = out + (size_t)blockIdx.x * inter;
     constexpr int VN = Vec16<T>::N;
@@ -160,13 +171,13 @@ __global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out
             load16(row + inter + i, u);
             T y[VN];
 #pragma unroll
-            for (int j = 0; j < VN; ++j) y[j] = from_f32<T>(clamped_glu(g[j], u[j], limit, slope));
+            for (int j = 0; j < VN; ++j) y[j] = from_f32<T>(clamped_glu(g[j], u[j], limit, slope, shift));
             *reinterpret_cast<uint4*>(o + i) = *reinterpret_cast<const uint4*>(y);
         }
         return;
     }
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < inter; i += gridDim.y * blockDim.x)
-        o[i] = from_f32<T>(clamped_glu(to_f32(row[i]), to_f32(row[inter + i]), limit, slope));
+        o[i] = from_f32<T>(clamped_glu(to_f32(row[i]), to_f32(row[inter + i]), limit, slope, shift));
 }
 
 // ------------------------------------------------------------------ sort the pairs by expert
@@ -207,7 +218,7 @@ constexpr int SM_ = 32, SN_ = 64, SK_ = 32;
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256) moe_gemm_simt_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, T* __restrict__ out, int ldo,
                                                             const int* __restrict__ sorted_pair, const int* __restrict__ tile_expert,
-                                                            int top, int N, int K, float limit, float slope) {
+                                                            int top, int N, int K, float limit, float slope, float shift) {
     const int e = tile_expert[blockIdx.x];
     if (e < 0) return;
     __shared__ float As[SM_][SK_ + 1], Bs[SN_][SK_ + 1], Bu[MODE == 0 ? SN_ : 1][SK_ + 1];
@@ -258,7 +269,7 @@ __global__ void __launch_bounds__(256) moe_gemm_simt_kernel(const T* __restrict_
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx + 16 * j;
-            if (n < N) out[dst * ldo + n] = from_f32<T>(MODE == 0 ? clamped_glu(acc[i][j], accu[i][j], limit, slope) : acc[i][j]);
+            if (n < N) out[dst * ldo + n] = from_f32<T>(MODE == 0 ? clamped_glu(acc[i][j], accu[i][j], limit, slope, shift) : acc[i][j]);
         }
     }
 }
@@ -287,7 +298,7 @@ constexpr int TK = 64, TROW = 72, TSTAGES = 3;                      // k per sta
 template <int MODE, int MT, int WM, int WN>
 __global__ void __launch_bounds__(256, 2) moe_gemm_tc_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W,
                                                           __nv_bfloat16* __restrict__ out, int ldo, const int* __restrict__ sorted_pair,
-                                                          const int* __restrict__ tile_expert, int top, int N, int K, float limit, float slope) {
+                                                          const int* __restrict__ tile_expert, int top, int N, int K, float limit, float slope, float shift) {
     constexpr int BM = 16 * MT * WM, WNE = 128 / WN, NT = WNE / 8, BN_OUT = MODE == 0 ? 64 : 128;
     const int e = tile_expert[blockIdx.x];
     if (e < 0) return;
@@ -372,8 +383,8 @@ __global__ void __launch_bounds__(256, 2) moe_gemm_tc_kernel(const __nv_bfloat16
                 for (int j = 0; j < NT / 2; ++j) {
                     const int col = n0 + wn * (WNE / 2) + j * 8 + c2;
                     if (col < N) {                                   // N is even: col + 1 < N as well
-                        const float y0 = clamped_glu(acc[i][j][half * 2], acc[i][j + NT / 2][half * 2], limit, slope);
-                        const float y1 = clamped_glu(acc[i][j][half * 2 + 1], acc[i][j + NT / 2][half * 2 + 1], limit, slope);
+                        const float y0 = clamped_glu(acc[i][j][half * 2], acc[i][j + NT / 2][half * 2], limit, slope, shift);
+                        const float y1 = clamped_glu(acc[i][j][half * 2 + 1], acc[i][j + NT / 2][half * 2 + 1], limit, slope, shift);
                         *reinterpret_cast<__nv_bfloat162*>(orow + col) = __floats2bfloat162_rn(y0, y1);
                     }
                 }
@@ -391,45 +402,65 @@ __global__ void __launch_bounds__(256, 2) moe_gemm_tc_kernel(const __nv_bfloat16
 // ------------------------------------------------------------------ weighted sum per token
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ rows, const float* __restrict__ weights, const T* __restrict__ shared,
-                                   T* __restrict__ out, int hidden, int top) {
+                                   const float* __restrict__ shared_gate, T* __restrict__ out, int hidden, int top) {
     const size_t t = blockIdx.x;
+    const float sg = shared_gate ? 1.f / (1.f + expf(-shared_gate[t])) : 1.f;      // the shared expert's row times sigmoid(its gate's logit)
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < hidden; c += gridDim.y * blockDim.x) {
         float acc = 0.f;
-        for (int j = 0; j < top; ++j) acc = fmaf(weights[t * top + j], to_f32(rows[(t * top + j) * hidden + c]), acc);
-        if (shared) acc += to_f32(shared[t * hidden + c]);
+        if (weights) for (int j = 0; j < top; ++j) acc = fmaf(weights[t * top + j], to_f32(rows[(t * top + j) * hidden + c]), acc);
+        else for (int j = 0; j < top; ++j) acc += to_f32(rows[(t * top + j) * hidden + c]);
+        if (shared) acc = fmaf(sg, to_f32(shared[t * hidden + c]), acc);
         out[t * hidden + c] = from_f32<T>(acc);
     }
 }
 
+// ------------------------------------------------------------------ row p = weight[p] * h[p / top]
+template <typename T>
+__global__ void moe_scale_rows_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ weights, int top, T* __restrict__ out, int K) {
+    const size_t p = blockIdx.x;
+    const float w = weights[p];
+    const T* src = h + (p / top) * ldh;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < K; c += gridDim.y * blockDim.x) out[p * K + c] = from_f32<T>(w * to_f32(src[c]));
+}
+
 }  // namespace
 
-// router [E, hidden] in the dtype of h (its values are read as they are stored and multiplied and added in float32)
+MI_EXPORT int mi_moe_scale_rows(const void* h, int ldh, const float* weights, int top, void* out, int P, int K, int dtype, cudaStream_t stream) {
+    if (P == 0) return 0;
+    dim3 grid(P, P >= 512 ? 1 : min(8, (K + 255) / 256));
+    if (dtype == MI_BF16) moe_scale_rows_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)h, ldh, weights, top, (__nv_bfloat16*)out, K);
+    else moe_scale_rows_kernel<float><<<grid, 256, 0, stream>>>((const float*)h, ldh, weights, top, (float*)out, K);
+    return (int)cudaGetLastError();
+}
+
+// router [E + extra, hidden] in the dtype of h (its values are read as they are stored and multiplied and added in float32)
 MI_EXPORT int mi_route_topk(const void* h, int ldh, const void* router, const float* corr, int* chosen, float* weights, int T_, int hidden,
-                            int E, int top, int g_count, int g_keep, int dtype, cudaStream_t stream) {
+                            int E, int top, int g_count, int g_keep, int sigmoid_scores, int extra, float* extra_out, int dtype,
+                            cudaStream_t stream) {
     if (T_ == 0) return 0;
-    if (top > E || (g_count > 0 && E % g_count)) return -2;
+    if (top > E || (g_count > 0 && E % g_count) || extra < 0 || (extra > 0 && !extra_out)) return -2;
     const int tok = T_ >= 1024 ? 8 : 1;
-    const size_t smem = ((size_t)tok * hidden + 3 * (size_t)tok * E) * sizeof(float);
+    const size_t smem = ((size_t)tok * hidden + 3 * (size_t)tok * (E + extra)) * sizeof(float);
     if (smem > 200 * 1024) return -2;
     const int grid = (T_ + tok - 1) / tok;
 #define GO(T, TOK) do { \
         if (smem > 48 * 1024) cudaFuncSetAttribute(route_topk_kernel<T, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        route_topk_kernel<T, TOK><<<grid, TOK == 1 ? min(1024, max(128, 32 * E)) : 256, smem, stream>>>((const T*)h, ldh, (const T*)router, corr, chosen, weights, T_, hidden, E, top, \
-                                                               g_count, g_keep); } while (0)
+        route_topk_kernel<T, TOK><<<grid, TOK == 1 ? min(1024, max(128, 32 * (E + extra))) : 256, smem, stream>>>((const T*)h, ldh, (const T*)router, corr, chosen, weights, T_, hidden, E, top, \
+                                                               g_count, g_keep, sigmoid_scores, extra, extra_out); } while (0)
     if (dtype == MI_BF16) { if (tok == 8) GO(__nv_bfloat16, 8); else GO(__nv_bfloat16, 1); }
     else { if (tok == 8) GO(float, 8); else GO(float, 1); }
 #undef GO
     return (int)cudaGetLastError();
 }
 
-MI_EXPORT int mi_clamped_glu(const void* gu, void* out, int rows, int inter, float limit, float slope, int dtype, cudaStream_t stream) {
+MI_EXPORT int mi_clamped_glu(const void* gu, void* out, int rows, int inter, float limit, float slope, float shift, int dtype, cudaStream_t stream) {
     if (rows == 0) return 0;
     const int vn = dtype == MI_BF16 ? 8 : 4;
     const int vec = inter % vn == 0 && ((uintptr_t)gu % 16) == 0 && ((uintptr_t)out % 16) == 0;
     const int per = vec ? 256 * vn : 256;
     dim3 grid(rows, rows >= 512 ? 1 : min(16, (inter + per - 1) / per));
-    if (dtype == MI_BF16) clamped_glu_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, limit, slope, vec);
-    else clamped_glu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)out, inter, limit, slope, vec);
+    if (dtype == MI_BF16) clamped_glu_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, limit, slope, shift, vec);
+    else clamped_glu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)out, inter, limit, slope, shift, vec);
     return (int)cudaGetLastError();
 }
 
@@ -446,12 +477,12 @@ MI_EXPORT int mi_moe_tile_rows_simt() { return SM_; }
 
 // mode 0: A = tokens [T, K], W [E, 2 N, K], out [cap_pos, N] activated; mode 1: A = [cap_pos, K], W [E, N, K], out [P, N]
 MI_EXPORT int mi_moe_gemm_simt(const void* A, int lda, const void* W, void* out, int ldo, const int* sorted_pair, const int* tile_expert,
-                               int cap_tiles, int top, int N, int K, float limit, float slope, int mode, int dtype, cudaStream_t stream) {
+                               int cap_tiles, int top, int N, int K, float limit, float slope, float shift, int mode, int dtype, cudaStream_t stream) {
     if (cap_tiles == 0) return 0;
     dim3 grid(cap_tiles, (N + SN_ - 1) / SN_);
     if (grid.y > 65535) return -2;
 #define GO(T, MODE) moe_gemm_simt_kernel<T, MODE><<<grid, 256, 0, stream>>>((const T*)A, lda, (const T*)W, (T*)out, ldo, sorted_pair, tile_expert, \
-                                                                           top, N, K, limit, slope)
+                                                                           top, N, K, limit, slope, shift)
     if (dtype == MI_BF16) { if (mode == 0) GO(__nv_bfloat16, 0); else GO(__nv_bfloat16, 1); }
     else { if (mode == 0) GO(float, 0); else GO(float, 1); }
 #undef GO
@@ -466,7 +497,7 @@ MI_EXPORT int mi_moe_tile_rows_tc(int P, int E) {
 
 // bfloat16 only; K % 64 == 0, N even, lda % 8 == 0; BM as mi_moe_tile_rows_tc said (and as mi_moe_align sorted)
 MI_EXPORT int mi_moe_gemm_tc(const void* A, int lda, const void* W, void* out, int ldo, const int* sorted_pair, const int* tile_expert,
-                             int cap_tiles, int top, int N, int K, float limit, float slope, int mode, int BM, int dtype, cudaStream_t stream) {
+                             int cap_tiles, int top, int N, int K, float limit, float slope, float shift, int mode, int BM, int dtype, cudaStream_t stream) {
     if (cap_tiles == 0) return 0;
     if (dtype != MI_BF16) return -1;
     if (K % TK || N % 2 || lda % 8 || ldo % 2) return -2;
@@ -477,7 +508,7 @@ MI_EXPORT int mi_moe_gemm_tc(const void* A, int lda, const void* W, void* out, i
         auto kern = moe_gemm_tc_kernel<MODE, MT, WM, WN>; \
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         kern<<<grid, 256, smem, stream>>>((const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, (__nv_bfloat16*)out, ldo, sorted_pair, \
-                                          tile_expert, top, N, K, limit, slope); } while (0)
+                                          tile_expert, top, N, K, limit, slope, shift); } while (0)
     if (BM == 128) { if (mode == 0) GO(0, 4, 2, 4); else GO(1, 4, 2, 4); }
     else if (BM == 64) { if (mode == 0) GO(0, 2, 2, 4); else GO(1, 2, 2, 4); }
     else if (BM == 16) { if (mode == 0) GO(0, 1, 1, 8); else GO(1, 1, 1, 8); }
@@ -486,13 +517,13 @@ MI_EXPORT int mi_moe_gemm_tc(const void* A, int lda, const void* W, void* out, i
     return (int)cudaGetLastError();
 }
 
-MI_EXPORT int mi_moe_combine(const void* rows, const float* weights, const void* shared, void* out, int T_, int hidden, int top, int dtype,
-                             cudaStream_t stream) {
+MI_EXPORT int mi_moe_combine(const void* rows, const float* weights, const void* shared, const float* shared_gate, void* out, int T_, int hidden,
+                             int top, int dtype, cudaStream_t stream) {
     if (T_ == 0) return 0;
     dim3 grid(T_, T_ >= 512 ? 1 : min(8, (hidden + 255) / 256));
     if (dtype == MI_BF16)
-        moe_combine_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)rows, weights, (const __nv_bfloat16*)shared, (__nv_bfloat16*)out, hidden, top);
+        moe_combine_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)rows, weights, (const __nv_bfloat16*)shared, shared_gate, (__nv_bfloat16*)out, hidden, top);
     else
-        moe_combine_kernel<float><<<grid, 256, 0, stream>>>((const float*)rows, weights, (const float*)shared, (float*)out, hidden, top);
+        moe_combine_kernel<float><<<grid, 256, 0, stream>>>((const float*)rows, weights, (const float*)shared, shared_gate, (float*)out, hidden, top);
     return (int)cudaGetLastError();
 }

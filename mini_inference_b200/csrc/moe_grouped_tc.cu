@@ -31,10 +31,10 @@ constexpr int GM = 128, GK = 64, GSTAGES = 2;
 constexpr int GA_BYTES = GM * GK * 2, GB_BYTES = 256 * GK * 2, GSTAGE_BYTES = GA_BYTES + GB_BYTES;
 constexpr int GTMEM_COLS = 256;
 
-__device__ __forceinline__ float gated(float g, float u, float limit, float slope) {
+__device__ __forceinline__ float gated(float g, float u, float limit, float slope, float shift) {
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
-    return g * __frcp_rn(1.f + __expf(-slope * g)) * (u + 1.f);
+    return g * __frcp_rn(1.f + __expf(-slope * g)) * (u + shift);
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -45,7 +45,7 @@ template <int MODE>
 __global__ void __launch_bounds__(256, 2)
 moe_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, __nv_bfloat16* __restrict__ out,
                         int ldo, const int* __restrict__ sorted_pair, const int* __restrict__ tile_expert, int N, int K, float limit,
-                        float slope, int* __restrict__ error_word) {
+                        float slope, float shift, int* __restrict__ error_word) {
     const int e = tile_expert[blockIdx.x];
     if (e < 0) return;
     extern __shared__ unsigned char gsm_raw[];
@@ -126,8 +126,8 @@ moe_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_c
                     uint32_t* wp = reinterpret_cast<uint32_t*>(&w);
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
-                        wp[j] = pack_bf16x2(gated(__uint_as_float(g[v4 * 8 + 2 * j]), __uint_as_float(u[v4 * 8 + 2 * j]), limit, slope),
-                                            gated(__uint_as_float(g[v4 * 8 + 2 * j + 1]), __uint_as_float(u[v4 * 8 + 2 * j + 1]), limit, slope));
+                        wp[j] = pack_bf16x2(gated(__uint_as_float(g[v4 * 8 + 2 * j]), __uint_as_float(u[v4 * 8 + 2 * j]), limit, slope, shift),
+                                            gated(__uint_as_float(g[v4 * 8 + 2 * j + 1]), __uint_as_float(u[v4 * 8 + 2 * j + 1]), limit, slope, shift));
                     if (pr >= 0 && col < N) *reinterpret_cast<uint4*>(orow + col) = w;
                 }
             }
@@ -157,7 +157,7 @@ moe_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap amap, const __grid_c
 
 // sorted[pos] = h[sorted_pair[pos] / top] (zeros where the position is padding): the rows of the first grouped product
 __global__ void moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ h, int ldh, const int* __restrict__ sorted_pair, int top,
-                                       __nv_bfloat16* __restrict__ sorted, int K) {
+                                       __nv_bfloat16* __restrict__ sorted, int K, const float* __restrict__ weights) {
     const int pr = sorted_pair[blockIdx.x];
     uint4* dst = reinterpret_cast<uint4*>(sorted + (size_t)blockIdx.x * K);
     if (pr < 0) {
@@ -165,22 +165,34 @@ __global__ void moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ h, int 
         return;
     }
     const uint4* src = reinterpret_cast<const uint4*>(h + (size_t)(pr / top) * ldh);
-    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) dst[i] = src[i];
+    if (!weights) {
+        for (int i = threadIdx.x; i < K / 8; i += blockDim.x) dst[i] = src[i];
+        return;
+    }
+    const float w = weights[pr];                                    // the pair's score multiplies the expert's input
+    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
+        uint4 raw = src[i];
+        __nv_bfloat162* v = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(v[j]); v[j] = __floats2bfloat162_rn(w * f.x, w * f.y); }
+        dst[i] = raw;
+    }
 }
 
 }  // namespace
 
-MI_EXPORT int mi_moe_gather_rows(const void* h, int ldh, const int* sorted_pair, int top, void* sorted, int cap_pos, int K, cudaStream_t stream) {
+MI_EXPORT int mi_moe_gather_rows(const void* h, int ldh, const int* sorted_pair, int top, void* sorted, int cap_pos, int K, const float* weights,
+                                 cudaStream_t stream) {
     if (cap_pos == 0) return 0;
     if (K % 8 || ldh % 8 || ((uintptr_t)h % 16) || ((uintptr_t)sorted % 16)) return -2;
-    moe_gather_rows_kernel<<<cap_pos, 128, 0, stream>>>((const __nv_bfloat16*)h, ldh, sorted_pair, top, (__nv_bfloat16*)sorted, K);
+    moe_gather_rows_kernel<<<cap_pos, 128, 0, stream>>>((const __nv_bfloat16*)h, ldh, sorted_pair, top, (__nv_bfloat16*)sorted, K, weights);
     return (int)cudaGetLastError();
 }
 
 // A [cap_tiles * 128, K] contiguous bfloat16 (sorted rows); W [E, mode 0 ? 2 N : N, K] contiguous; out: mode 0 [cap_tiles * 128, N]
 // (ldo = N), mode 1 [pairs, N].  K % 64 == 0, N % 8 == 0.
 MI_EXPORT int mi_moe_gemm_tcgen05(const void* A, const void* W, int E, void* out, int ldo, const int* sorted_pair, const int* tile_expert,
-                                  int cap_tiles, int N, int K, float limit, float slope, int mode, int* error_word, cudaStream_t stream) {
+                                  int cap_tiles, int N, int K, float limit, float slope, float shift, int mode, int* error_word, cudaStream_t stream) {
     if (cap_tiles == 0) return 0;
     if (K % GK || K < GK || N % 8 || ldo % 8 || ((uintptr_t)A % 16) || ((uintptr_t)W % 16) || ((uintptr_t)out % 16)) return -2;
     CUtensorMap amap, bmap;
@@ -197,7 +209,7 @@ MI_EXPORT int mi_moe_gemm_tcgen05(const void* A, const void* W, int E, void* out
             configured[MODE] = true; \
         } \
         moe_gemm_tcgen05_kernel<MODE><<<grid, 256, smem, stream>>>(amap, bmap, (__nv_bfloat16*)out, ldo, sorted_pair, tile_expert, N, K, limit, \
-                                                                  slope, error_word); } while (0)
+                                                                  slope, shift, error_word); } while (0)
     if (mode == 0) GO(0); else GO(1);
 #undef GO
     return (int)cudaGetLastError();

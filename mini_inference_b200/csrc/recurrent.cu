@@ -31,7 +31,7 @@ constexpr int SCAN_THREADS = 128;
 // LN lanes share a pair of columns (8: a warp holds 4 pairs, the state moves in 32-byte pieces, few blocks: decode steps,
 // where the state's bytes are the cost; 16 or 32: fewer rows per lane, so a token's chain of dependent instructions is
 // shorter and more warps share the work: prompt portions, where the tokens' latency is the cost).  Columns per block:
-constexpr int cols_of(int LN) { return 4 * (32 / LN) * 2; }
+__host__ __device__ constexpr int cols_of(int LN) { return 4 * (32 / LN) * 2; }
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + expf(-x)); }
 __device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + expf(-x)); }
@@ -43,20 +43,33 @@ __device__ __forceinline__ void cp16(float* dst, const float* src) {
 __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;\n" :: "n"(N) : "memory"); }
 
+// Forms of the recurrence (MODE):
+//   0  S <- decay[h] S + k v^T                                   (one constant per head)
+//   1  S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T       (rows q, k, g; one number beta per token and head)
+//   2  S <- diag(g) S - c (u^T S) + k v^T, both terms reading the old S   (rows q, k, g, u, c = removal rate times u)
+//   3  S <- f S + k v^T with one number f per token and head      (rows q, k; k arrives already multiplied by its input gate)
+// always followed by o = S^T q.
+__host__ __device__ constexpr int rows_of(int MODE) { return MODE == 1 ? 3 : MODE == 2 ? 5 : 2; }
+__host__ __device__ constexpr bool scalar_of(int MODE) { return MODE == 1 || MODE == 3; }
+
 // Where the scan finds a token's numbers in its float32 row (ld floats per token).
 struct ScanLayout {
-    int ld, q_off, k_off, v_off, g_off, b_off;      // q/k: + kv_head * D; v: + head * V; g: + head * D; beta: + head
+    int ld, q_off, k_off, v_off, g_off, b_off;      // q/k: + kv_head * D; v: + head * V; g: + head * D; the per-token number (beta or f): + head
+    int u_off, c_off;                               // MODE 2: + head * D
 };
 
-// One chunk of nt tokens into a buffer: q, k (g) rows of Dp floats (D copied, the rest stays zero), v [COLS], beta.
-template <bool DELTA, int COLS>
+// One chunk of nt tokens into a buffer: rows of Dp floats (D copied, the rest stays zero), v [COLS], the per-token number.
+template <int MODE, int COLS>
 __device__ __forceinline__ void stage_chunk(float* buf, int Dp, int TC, const float* __restrict__ prep, const ScanLayout L,
                                             int tok0, int nt, int h, int kvh, int D, int V, int col0, bool vec) {
+    constexpr int NR = rows_of(MODE);
     float* qsm = buf;
     float* ksm = qsm + TC * Dp;
-    float* gsm = ksm + TC * Dp;                               // DELTA only
-    float* vsm = DELTA ? gsm + TC * Dp : ksm + TC * Dp;       // [TC, COLS]
-    float* bsm = vsm + TC * COLS;                             // [TC] (DELTA only)
+    float* gsm = ksm + TC * Dp;                               // MODE 1, 2
+    float* usm = gsm + TC * Dp;                               // MODE 2
+    float* csm = usm + TC * Dp;                               // MODE 2
+    float* vsm = buf + NR * TC * Dp;                          // [TC, COLS]
+    float* bsm = vsm + TC * COLS;                             // [TC] (MODE 1, 3)
     const int ncol = min(COLS, V - col0);
     if (vec) {
         const int dq = D >> 2, vq = ncol >> 2;
@@ -65,7 +78,8 @@ __device__ __forceinline__ void stage_chunk(float* buf, int Dp, int TC, const fl
             const float* row = prep + (size_t)(tok0 + tt) * L.ld;
             cp16(qsm + tt * Dp + c, row + L.q_off + kvh * D + c);
             cp16(ksm + tt * Dp + c, row + L.k_off + kvh * D + c);
-            if (DELTA) cp16(gsm + tt * Dp + c, row + L.g_off + h * D + c);
+            if (MODE == 1 || MODE == 2) cp16(gsm + tt * Dp + c, row + L.g_off + h * D + c);
+            if (MODE == 2) { cp16(usm + tt * Dp + c, row + L.u_off + h * D + c); cp16(csm + tt * Dp + c, row + L.c_off + h * D + c); }
         }
         for (int idx = threadIdx.x; idx < nt * vq; idx += SCAN_THREADS) {
             const int tt = idx / vq, c = (idx - tt * vq) << 2;
@@ -77,14 +91,15 @@ __device__ __forceinline__ void stage_chunk(float* buf, int Dp, int TC, const fl
             const float* row = prep + (size_t)(tok0 + tt) * L.ld;
             qsm[tt * Dp + c] = row[L.q_off + kvh * D + c];
             ksm[tt * Dp + c] = row[L.k_off + kvh * D + c];
-            if (DELTA) gsm[tt * Dp + c] = row[L.g_off + h * D + c];
+            if (MODE == 1 || MODE == 2) gsm[tt * Dp + c] = row[L.g_off + h * D + c];
+            if (MODE == 2) { usm[tt * Dp + c] = row[L.u_off + h * D + c]; csm[tt * Dp + c] = row[L.c_off + h * D + c]; }
         }
         for (int idx = threadIdx.x; idx < nt * ncol; idx += SCAN_THREADS) {
             const int tt = idx / ncol, c = idx - tt * ncol;
             vsm[tt * COLS + c] = prep[(size_t)(tok0 + tt) * L.ld + L.v_off + h * V + col0 + c];
         }
     }
-    if (DELTA)
+    if (scalar_of(MODE))
         for (int tt = threadIdx.x; tt < nt; tt += SCAN_THREADS) bsm[tt] = prep[(size_t)(tok0 + tt) * L.ld + L.b_off + h];
 }
 
@@ -100,16 +115,16 @@ __device__ __forceinline__ float2 reduce_pair(float a0, float a1, int l) {
     return odd ? make_float2(other, keep) : make_float2(keep, other);
 }
 
-// grid (entries, heads, ceil(V / cols_of(LN))).  DELTA:  S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.
-// otherwise:  S <- decay[h] S + k v^T; o = S^T q.   NG: groups of four rows per lane (key_dim <= 4 LN NG).
-template <bool DELTA, int LN, int NG>
+// grid (entries, heads, ceil(V / cols_of(LN))).  NG: groups of four rows per lane (key_dim <= 4 LN NG).
+template <int MODE, int LN, int NG>
 __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(
         const float* __restrict__ prep, const ScanLayout L, const float* __restrict__ decay, float* __restrict__ state,
         long long state_stride, float* __restrict__ out, const int* __restrict__ seg_q_start, const int* __restrict__ seg_slot,
         int H, int KV, int D, int V, int TC, int vec) {
     extern __shared__ __align__(16) float sm[];
-    constexpr int LANES = LN, COLS = cols_of(LN), Dp = 4 * LN * NG;
-    const int buf_floats = TC * ((DELTA ? 3 : 2) * Dp + COLS + (DELTA ? 1 : 0));
+    constexpr int LANES = LN, COLS = cols_of(LN), Dp = 4 * LN * NG, NR = rows_of(MODE);
+    constexpr bool DELTA = MODE == 1;
+    const int buf_floats = TC * (NR * Dp + COLS + (scalar_of(MODE) ? 1 : 0));
     const int buf_stride = (buf_floats + 3) & ~3;
     float* part = sm + 2 * buf_stride;                         // [TC, COLS, LN + 1] partial sums of the read-out
     const int seg = blockIdx.x, h = blockIdx.y, kvh = h / (H / KV);
@@ -122,7 +137,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(
     __syncthreads();
     // the first chunk's copies start before the state is fetched, so that the two waits for global memory overlap
     const int chunks = (n + TC - 1) / TC;
-    stage_chunk<DELTA, COLS>(sm, Dp, TC, prep, L, qs, min(TC, n), h, kvh, D, V, col0, (vec & 1) != 0);
+    stage_chunk<MODE, COLS>(sm, Dp, TC, prep, L, qs, min(TC, n), h, kvh, D, V, col0, (vec & 1) != 0);
     cp_commit();
     float s0[4 * NG], s1[4 * NG];
 #pragma unroll
@@ -138,11 +153,11 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(
                 s1[4 * g + e] = (r < D && v1) ? S[(size_t)r * V + col + 1] : 0.f;
             }
         }
-    const float dec = DELTA ? 0.f : decay[h];
+    float dec = MODE == 0 ? decay[h] : 0.f;
     for (int c = 0; c < chunks; ++c) {
         const int t0 = c * TC, nt = min(TC, n - t0);
         if (c + 1 < chunks) {
-            stage_chunk<DELTA, COLS>(sm + ((c + 1) & 1) * buf_stride, Dp, TC, prep, L, qs + t0 + TC, min(TC, n - t0 - TC), h, kvh, D, V, col0, (vec & 1) != 0);
+            stage_chunk<MODE, COLS>(sm + ((c + 1) & 1) * buf_stride, Dp, TC, prep, L, qs + t0 + TC, min(TC, n - t0 - TC), h, kvh, D, V, col0, (vec & 1) != 0);
             cp_commit();
             cp_wait<1>();
         } else {
@@ -153,7 +168,9 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(
         const float* qsm = buf;
         const float* ksm = qsm + TC * Dp;
         const float* gsm = ksm + TC * Dp;
-        const float* vsm = DELTA ? gsm + TC * Dp : ksm + TC * Dp;
+        const float* usm = gsm + TC * Dp;
+        const float* csm = usm + TC * Dp;
+        const float* vsm = buf + NR * TC * Dp;
         const float* bsm = vsm + TC * COLS;
         // two partial sums per dot product and column keep the chains of dependent additions short
         for (int tt = 0; tt < nt; ++tt) {
@@ -189,7 +206,34 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(
                     b0 = fmaf(s1[4 * g], qv.x, b0); b1 = fmaf(s1[4 * g + 1], qv.y, b1);
                     b0 = fmaf(s1[4 * g + 2], qv.z, b0); b1 = fmaf(s1[4 * g + 3], qv.w, b1);
                 }
+            } else if (MODE == 2) {
+                const float4* gg = reinterpret_cast<const float4*>(gsm + tt * Dp) + l;
+                const float4* uu = reinterpret_cast<const float4*>(usm + tt * Dp) + l;
+                const float4* cc = reinterpret_cast<const float4*>(csm + tt * Dp) + l;
+                float d0 = 0.f, d1 = 0.f, e0 = 0.f, e1 = 0.f;
+#pragma unroll
+                for (int g = 0; g < NG; ++g) {                            // what the unit key sees of the old state
+                    const float4 uv = uu[LANES * g];
+                    d0 = fmaf(s0[4 * g], uv.x, d0); d1 = fmaf(s0[4 * g + 1], uv.y, d1);
+                    d0 = fmaf(s0[4 * g + 2], uv.z, d0); d1 = fmaf(s0[4 * g + 3], uv.w, d1);
+                    e0 = fmaf(s1[4 * g], uv.x, e0); e1 = fmaf(s1[4 * g + 1], uv.y, e1);
+                    e0 = fmaf(s1[4 * g + 2], uv.z, e0); e1 = fmaf(s1[4 * g + 3], uv.w, e1);
+                }
+                const float2 dot = reduce_pair<LN>(d0 + d1, e0 + e1, l);
+#pragma unroll
+                for (int g = 0; g < NG; ++g) {
+                    const float4 gv = gg[LANES * g], cv = cc[LANES * g], kv = kk[LANES * g], qv = qq[LANES * g];
+                    s0[4 * g] = fmaf(gv.x, s0[4 * g], fmaf(-cv.x, dot.x, kv.x * vv.x)); s0[4 * g + 1] = fmaf(gv.y, s0[4 * g + 1], fmaf(-cv.y, dot.x, kv.y * vv.x));
+                    s0[4 * g + 2] = fmaf(gv.z, s0[4 * g + 2], fmaf(-cv.z, dot.x, kv.z * vv.x)); s0[4 * g + 3] = fmaf(gv.w, s0[4 * g + 3], fmaf(-cv.w, dot.x, kv.w * vv.x));
+                    s1[4 * g] = fmaf(gv.x, s1[4 * g], fmaf(-cv.x, dot.y, kv.x * vv.y)); s1[4 * g + 1] = fmaf(gv.y, s1[4 * g + 1], fmaf(-cv.y, dot.y, kv.y * vv.y));
+                    s1[4 * g + 2] = fmaf(gv.z, s1[4 * g + 2], fmaf(-cv.z, dot.y, kv.z * vv.y)); s1[4 * g + 3] = fmaf(gv.w, s1[4 * g + 3], fmaf(-cv.w, dot.y, kv.w * vv.y));
+                    a0 = fmaf(s0[4 * g], qv.x, a0); a1 = fmaf(s0[4 * g + 1], qv.y, a1);
+                    a0 = fmaf(s0[4 * g + 2], qv.z, a0); a1 = fmaf(s0[4 * g + 3], qv.w, a1);
+                    b0 = fmaf(s1[4 * g], qv.x, b0); b1 = fmaf(s1[4 * g + 1], qv.y, b1);
+                    b0 = fmaf(s1[4 * g + 2], qv.z, b0); b1 = fmaf(s1[4 * g + 3], qv.w, b1);
+                }
             } else {
+                if (MODE == 3) dec = bsm[tt];
 #pragma unroll
                 for (int g = 0; g < NG; ++g) {
                     const float4 kv = kk[LANES * g], qv = qq[LANES * g];
@@ -231,28 +275,30 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(
         }
 }
 
-template <bool DELTA>
+template <int MODE>
 int launch_scan(const float* prep, ScanLayout L, const float* decay, float* state, long long state_stride, float* out,
                 const int* seg_q_start, const int* seg_slot, int T_, int num_segs, int H, int KV, int D, int V, cudaStream_t stream) {
     if (num_segs == 0) return 0;
     if (D > 256 || H > 65535) return -2;
+    constexpr int NR = rows_of(MODE);
     // entries of many tokens: as many lanes per column pair as leave a lane one group of four rows (up to a warp);
     // decode steps: 8 lanes, so that a warp moves the state in whole sectors
     int LN = 8;
     if (T_ > 4 * num_segs) LN = D > 64 ? 32 : D > 32 ? 16 : 8;
-    const int NG = (D + 4 * LN - 1) / (4 * LN);
+    int NG = (D + 4 * LN - 1) / (4 * LN);
+    if (LN == 8) NG = NG <= 2 ? NG : NG <= 4 ? 4 : 8;                      // the forms that exist: the kernel's rows have 4 LN NG floats
     const int COLS = cols_of(LN);
-    const int per_token = (DELTA ? 3 : 2) * 4 * LN * NG + COLS + 1;
+    const int per_token = NR * 4 * LN * NG + COLS + 1;
     const int per_chunk_token = 2 * per_token + COLS * (LN + 1);          // two staging buffers and the partial sums
     const int TC = T_ <= 4 * num_segs ? 4 : per_chunk_token * 16 * 4 <= 96 * 1024 ? 16 : per_chunk_token * 8 * 4 <= 96 * 1024 ? 8 : 4;   // decode steps: small buffers, more blocks per SM
     const size_t smem = (2 * (size_t)((TC * per_token + 3) & ~3) + (size_t)TC * COLS * (LN + 1)) * sizeof(float);
     // 16-byte copies need every piece on a 16-byte boundary: sizes and offsets in multiples of four floats
     const int vec = (((uintptr_t)prep % 16 == 0 && D % 4 == 0 && V % 4 == 0 && L.ld % 4 == 0 && L.q_off % 4 == 0 && L.k_off % 4 == 0 &&
-                     L.v_off % 4 == 0 && (!DELTA || L.g_off % 4 == 0)) ? 1 : 0)
+                     L.v_off % 4 == 0 && (!(MODE == 1 || MODE == 2) || L.g_off % 4 == 0) && (MODE != 2 || (L.u_off % 4 == 0 && L.c_off % 4 == 0))) ? 1 : 0)
                   | ((V % 2 == 0 && state_stride % 2 == 0 && (uintptr_t)state % 8 == 0) ? 2 : 0);      // bit 1: the state in 8-byte pairs
     dim3 grid(num_segs, H, (V + COLS - 1) / COLS);
 #define GO(LN_, N) do { \
-        auto kern = state_scan_kernel<DELTA, LN_, N>; \
+        auto kern = state_scan_kernel<MODE, LN_, N>; \
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); \
         kern<<<grid, SCAN_THREADS, smem, stream>>>(prep, L, decay, state, state_stride, out, seg_q_start, seg_slot, H, KV, D, V, TC, vec); } while (0)
     if (LN == 32) { if (NG == 1) GO(32, 1); else GO(32, 2); }
@@ -370,6 +416,236 @@ __global__ void conv_tail_kernel(const T* __restrict__ p, int ldp, float* __rest
     }
 }
 
+
+// ------------------------------------------------------------------ short causal convolution over time, per channel
+// out[t, c] = act(sum_j w[c, j] x(t - taps + 1 + j, c) + bias[c]) (+ x(t, c) when residual), x before an entry's first token
+// read from hist = state[slot] + hist_off, [taps - 1, C] (zeros for a request's first entry).  conv_tail_kernel then
+// moves the entry's newest inputs into the slot.
+template <typename T>
+__global__ void short_conv_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w, const float* __restrict__ bias,
+                                  const float* __restrict__ state, long long state_stride, long long hist_off, T* __restrict__ out,
+                                  const int* __restrict__ token_seg, const int* __restrict__ seg_q_start, const int* __restrict__ seg_slot,
+                                  int C, int taps, int residual, int act) {
+    const int t = blockIdx.x, seg = token_seg[t], qs = seg_q_start[seg], r = t - qs;
+    const float* hist = taps > 1 ? state + (long long)seg_slot[seg] * state_stride + hist_off : nullptr;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int off = r - (taps - 1 - j);
+            const float x = off >= 0 ? to_f32(h[(size_t)(qs + off) * ldh + c]) : hist[(size_t)(taps - 1 + off) * C + c];
+            acc = fmaf(w[(size_t)c * taps + j], x, acc);
+        }
+        if (bias) acc += bias[c];
+        if (act == 1) acc = silu(acc);
+        if (residual) acc += to_f32(h[(size_t)t * ldh + c]);
+        out[(size_t)t * C + c] = from_f32<T>(acc);
+    }
+}
+
+// ------------------------------------------------------------------ general delta rule, prologue
+// p [T, ldp] = r | k | v | a | g | low (H D, H D, H V, H D, H V, rank columns).  A block takes TOK neighbouring tokens and a
+// range of channels: low = tanh(.), decay = exp(-decay_scale sigmoid(w2 low + w0)) with w2 [H D, rank] read once for the
+// TOK tokens, removal a = sigmoid(. + a_b), unit key u = k / sqrt(sum k^2 + unit_eps) per head.
+// out [T, ldo] float32 = r | k | u | a u | decay | v.
+template <typename T, int TOK>
+__global__ void __launch_bounds__(256) general_delta_prepare_kernel(const T* __restrict__ p, int ldp, const T* __restrict__ w2,
+                                                                    const float* __restrict__ w0, const float* __restrict__ a_b,
+                                                                    float* __restrict__ out, int ldo, int T_, int H, int D, int V, int rank,
+                                                                    float decay_scale, float unit_eps) {
+    extern __shared__ __align__(16) float gsm[];
+    float* low_s = gsm;                              // [TOK][rank]
+    float* inv_s = low_s + TOK * rank;               // [TOK][H]
+    const int HD = H * D, HV = H * V, t0 = blockIdx.x * TOK, nt = min(TOK, T_ - t0);
+    const int a_off = 2 * HD + HV, low_off = 3 * HD + 2 * HV;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < TOK * rank; i += 256) {
+        const int k = i / rank, j = i - k * rank;
+        low_s[i] = k < nt ? tanhf(to_f32(p[(size_t)(t0 + k) * ldp + low_off + j])) : 0.f;
+    }
+    for (int u = warp; u < nt * H; u += 8) {
+        const int k = u / H, hh = u - k * H;
+        const T* kr = p + (size_t)(t0 + k) * ldp + HD + hh * D;
+        float ss = 0.f;
+        for (int d = lane; d < D; d += 32) { const float v = to_f32(kr[d]); ss += v * v; }
+        ss = warp_sum(ss);
+        if (lane == 0) inv_s[k * H + hh] = 1.f / sqrtf(ss + unit_eps);
+    }
+    __syncthreads();
+    for (int i = blockIdx.y * 256 + threadIdx.x; i < HD; i += gridDim.y * 256) {
+        float acc[TOK];
+#pragma unroll
+        for (int k = 0; k < TOK; ++k) acc[k] = 0.f;
+        const T* wr = w2 + (size_t)i * rank;
+        for (int j = 0; j < rank; ++j) {
+            const float wv = to_f32(wr[j]);
+#pragma unroll
+            for (int k = 0; k < TOK; ++k) acc[k] = fmaf(low_s[k * rank + j], wv, acc[k]);
+        }
+        const float b0 = w0[i], ab = a_b[i];
+        const int hh = i / D;
+#pragma unroll
+        for (int k = 0; k < TOK; ++k) {
+            if (k >= nt) break;
+            const T* row = p + (size_t)(t0 + k) * ldp;
+            float* o = out + (size_t)(t0 + k) * ldo;
+            const float kv = to_f32(row[HD + i]), u = kv * inv_s[k * H + hh];
+            o[i] = to_f32(row[i]);
+            o[HD + i] = kv;
+            o[2 * HD + i] = u;
+            o[3 * HD + i] = sigmoidf(to_f32(row[a_off + i]) + ab) * u;
+            o[4 * HD + i] = expf(-decay_scale * sigmoidf(acc[k] + b0));
+        }
+    }
+    for (int i = blockIdx.y * 256 + threadIdx.x; i < nt * HV; i += gridDim.y * 256) {
+        const int k = i / HV, c = i - k * HV;
+        out[(size_t)(t0 + k) * ldo + 5 * HD + c] = to_f32(p[(size_t)(t0 + k) * ldp + 2 * HD + c]);
+    }
+}
+
+// ------------------------------------------------------------------ matrix memory with exponential gates
+// (1) per token and head, in parallel: the capped gate logits -> log input gate i and log forget gate f = logsigmoid(.)
+__global__ void memory_gates_kernel(const float* __restrict__ gl, const float* __restrict__ bias, float* __restrict__ lg, int n, int H,
+                                    float cap, int capped) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const int c = idx % (2 * H);
+    float z = gl[idx] + bias[c];
+    if (capped) z = cap * tanhf(z / cap);
+    if (c >= H) z = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));          // logsigmoid
+    lg[idx] = z;
+}
+
+// (2) per (entry, head), in order: m' = max(f + m, i) from the slot's m; lg becomes [f + m - m' | i - m'] and mneg = -m'
+__global__ void memory_max_kernel(float* __restrict__ lg, float* __restrict__ mneg, float* __restrict__ state, long long state_stride,
+                                  long long m_off, const int* __restrict__ seg_q_start, const int* __restrict__ seg_slot, int H) {
+    const int seg = blockIdx.x, qs = seg_q_start[seg], n = seg_q_start[seg + 1] - qs;
+    float* ms = state + (long long)seg_slot[seg] * state_stride + m_off;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        float m = ms[h];
+#pragma unroll 4
+        for (int t = qs; t < qs + n; ++t) {
+            const float i = lg[(size_t)t * 2 * H + h], f = lg[(size_t)t * 2 * H + H + h];
+            const float mn = fmaxf(f + m, i);
+            lg[(size_t)t * 2 * H + h] = i - mn;
+            lg[(size_t)t * 2 * H + H + h] = f + m - mn;
+            mneg[(size_t)t * H + h] = -mn;
+            m = mn;
+        }
+        ms[h] = m;
+    }
+}
+
+// (3) per token: what the scan stages, float32: q * q_scale | e^(i - m') k | per head [v, 1, 0, 0, 0] | e^(f + m - m') per head
+template <typename T>
+__global__ void memory_prepare_kernel(const T* __restrict__ p, int ldp, const float* __restrict__ lg, float* __restrict__ out, int ldo,
+                                      int H, int D, int V, float q_scale) {
+    const size_t t = blockIdx.x;
+    const T* row = p + t * ldp;
+    float* o = out + t * ldo;
+    const float* g = lg + t * 2 * H;
+    const int HD = H * D, W = V + 4;
+    for (int i = threadIdx.x; i < HD; i += blockDim.x) {
+        o[i] = to_f32(row[i]) * q_scale;
+        o[HD + i] = to_f32(row[HD + i]) * expf(g[i / D]);
+    }
+    for (int i = threadIdx.x; i < H * W; i += blockDim.x) {
+        const int hh = i / W, c = i - hh * W;
+        o[2 * HD + i] = c < V ? to_f32(row[2 * HD + hh * V + c]) : c == V ? 1.f : 0.f;
+    }
+    for (int hh = threadIdx.x; hh < H; hh += blockDim.x) o[2 * HD + H * W + hh] = expf(g[H + hh]);
+}
+
+// (4) per (token, head): o = full[:V] / (max(|full[V]|, e^(-m)) + den_eps); rows = o / rms(o) * weight * sigmoid(gate)
+template <typename T>
+__global__ void memory_output_kernel(const float* __restrict__ full, const float* __restrict__ mneg, const float* __restrict__ w,
+                                     const T* __restrict__ gate, int gate_stride, T* __restrict__ y, int H, int V, float den_eps, float eps) {
+    const size_t t = blockIdx.x;
+    const int hh = blockIdx.y, lane = threadIdx.x;
+    const float* f = full + (t * H + hh) * (V + 4);
+    const float den = fmaxf(fabsf(f[V]), expf(mneg[t * H + hh])) + den_eps;
+    float ss = 0.f;
+    for (int v = lane; v < V; v += 32) { const float o = f[v] / den; ss += o * o; }
+    const float r = rsqrtf(warp_sum(ss) / V + eps);
+    for (int v = lane; v < V; v += 32) {
+        const float sg = sigmoidf(to_f32(gate[t * gate_stride + hh * V + v]));
+        y[t * H * V + hh * V + v] = from_f32<T>(f[v] / den * r * w[hh * V + v] * sg);
+    }
+}
+
+// ------------------------------------------------------------------ selective state-space scan
+// grid (entries, ceil(I / 32)), 256 threads: 8 lanes share a channel, lane l holding the states n = l + 8 g in registers.
+// Per chunk of SS_TC tokens the block stages B and C [N] of each token, and for its 32 channels the step softplus(dt + dt_b),
+// x and z, all float32.  S <- exp(step A) S + step x B;  y = sum_n S C + D x;  out = y * silu(z).
+constexpr int SS_TC = 16;
+template <typename T, int NG>
+__global__ void __launch_bounds__(256) selective_scan_kernel(const T* __restrict__ x, const float* __restrict__ dt, const float* __restrict__ dt_b,
+                                                             const float* __restrict__ A, const T* __restrict__ B, int ldb,
+                                                             const T* __restrict__ Cm, int ldc, const float* __restrict__ Dv,
+                                                             const T* __restrict__ z, int ldz, float* __restrict__ state, long long state_stride,
+                                                             T* __restrict__ out, const int* __restrict__ seg_q_start,
+                                                             const int* __restrict__ seg_slot, int I, int N) {
+    extern __shared__ __align__(16) float ssm[];
+    float* Bs = ssm;                        // [SS_TC][N]
+    float* Cs = Bs + SS_TC * N;             // [SS_TC][N]
+    float* st = Cs + SS_TC * N;             // [SS_TC][32] step
+    float* xs = st + SS_TC * 32;            // [SS_TC][32]
+    float* zs = xs + SS_TC * 32;            // [SS_TC][32]
+    const int seg = blockIdx.x, qs = seg_q_start[seg], n = seg_q_start[seg + 1] - qs;
+    const int c0 = blockIdx.y * 32, cl = threadIdx.x >> 3, l = threadIdx.x & 7, c = c0 + cl;
+    const bool live = c < I;
+    float* S = state + (long long)seg_slot[seg] * state_stride + (size_t)(live ? c : 0) * N;
+    float s[NG], a[NG];
+#pragma unroll
+    for (int g = 0; g < NG; ++g) {
+        const int nn = l + 8 * g;
+        const bool ok = live && nn < N;
+        s[g] = ok ? S[nn] : 0.f;
+        a[g] = ok ? A[(size_t)c * N + nn] : 0.f;
+    }
+    const float dv = live ? Dv[c] : 0.f;
+    for (int t0 = 0; t0 < n; t0 += SS_TC) {
+        const int nt = min(SS_TC, n - t0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nt * N; i += 256) {
+            const int tt = i / N, nn = i - tt * N;
+            Bs[i] = to_f32(B[(size_t)(qs + t0 + tt) * ldb + nn]);
+            Cs[i] = to_f32(Cm[(size_t)(qs + t0 + tt) * ldc + nn]);
+        }
+        for (int i = threadIdx.x; i < nt * 32; i += 256) {
+            const int tt = i >> 5, cc = c0 + (i & 31);
+            if (cc < I) {
+                const size_t tok = qs + t0 + tt;
+                const float v = dt[tok * I + cc] + dt_b[cc];
+                st[i] = v > 20.f ? v : log1pf(expf(v));
+                xs[i] = to_f32(x[tok * I + cc]);
+                zs[i] = to_f32(z[tok * ldz + cc]);
+            }
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float step = st[tt * 32 + cl], xv = xs[tt * 32 + cl], sx = step * xv;
+            float y = 0.f;
+#pragma unroll
+            for (int g = 0; g < NG; ++g) {
+                const int nn = l + 8 * g;
+                if (nn < N) {
+                    s[g] = fmaf(expf(step * a[g]), s[g], sx * Bs[tt * N + nn]);
+                    y = fmaf(s[g], Cs[tt * N + nn], y);
+                }
+            }
+            y += __shfl_xor_sync(0xffffffffu, y, 1);
+            y += __shfl_xor_sync(0xffffffffu, y, 2);
+            y += __shfl_xor_sync(0xffffffffu, y, 4);
+            if (l == 0 && live) out[(size_t)(qs + t0 + tt) * I + c] = from_f32<T>((y + dv * xv) * silu(zs[tt * 32 + cl]));
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < NG; ++g) {
+        const int nn = l + 8 * g;
+        if (live && nn < N) S[nn] = s[g];
+    }
+}
+
 }  // namespace
 
 // p [T, ldp] = q | k | v before silu (2 H D + H V columns); prep: float32 scratch [T, 2 H D + H V]; out float32 [T, H V].
@@ -383,8 +659,8 @@ MI_EXPORT int mi_lightning_scan(const void* p, int ldp, float* prep, const float
     else silu_f32_kernel<float><<<pgrid, 256, 0, stream>>>((const float*)p, ldp, prep, n);
     int err = (int)cudaGetLastError();
     if (err) return err;
-    ScanLayout L{n, 0, H * D, 2 * H * D, 0, 0};
-    return launch_scan<false>(prep, L, decay, state, state_stride, out, seg_q_start, seg_slot, T_, num_segs, H, H, D, V, stream);
+    ScanLayout L{n, 0, H * D, 2 * H * D, 0, 0, 0, 0};
+    return launch_scan<0>(prep, L, decay, state, state_stride, out, seg_q_start, seg_slot, T_, num_segs, H, H, D, V, stream);
 }
 
 // p [T, ldp] = q | k | v as projected; inv_freq: half frequencies (nullptr or half = 0: no rotation).  Otherwise as mi_lightning_scan.
@@ -399,15 +675,15 @@ MI_EXPORT int mi_retention_scan(const void* p, int ldp, float* prep, const int* 
     else rotate_f32_kernel<float><<<pgrid, 256, 0, stream>>>((const float*)p, ldp, prep, positions, inv_freq, inv_freq ? half : 0, k_scale, H, D, V);
     int err = (int)cudaGetLastError();
     if (err) return err;
-    ScanLayout L{n, 0, H * D, 2 * H * D, 0, 0};
-    return launch_scan<false>(prep, L, decay, state, state_stride, out, seg_q_start, seg_slot, T_, num_segs, H, H, D, V, stream);
+    ScanLayout L{n, 0, H * D, 2 * H * D, 0, 0, 0, 0};
+    return launch_scan<0>(prep, L, decay, state, state_stride, out, seg_q_start, seg_slot, T_, num_segs, H, H, D, V, stream);
 }
 
 MI_EXPORT int mi_delta_scan(const float* prep, int ld, float* state, long long state_stride, float* out, const int* seg_q_start,
                             const int* seg_slot, int T_, int num_segs, int H, int KV, int D, int V, cudaStream_t stream) {
     const int C = 2 * KV * D + H * V;
-    ScanLayout L{ld, 0, KV * D, 2 * KV * D, C, C + H * D};
-    return launch_scan<true>(prep, L, nullptr, state, state_stride, out, seg_q_start, seg_slot, T_, num_segs, H, KV, D, V, stream);
+    ScanLayout L{ld, 0, KV * D, 2 * KV * D, C, C + H * D, 0, 0};
+    return launch_scan<1>(prep, L, nullptr, state, state_stride, out, seg_q_start, seg_slot, T_, num_segs, H, KV, D, V, stream);
 }
 
 MI_EXPORT int mi_delta_prepare(const void* p, int ldp, const void* a, int lda, const float* conv, const float* A_log, const float* dt_bias,
@@ -434,5 +710,99 @@ MI_EXPORT int mi_delta_prepare(const void* p, int ldp, const void* a, int lda, c
         conv_tail_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)p, ldp, state, state_stride, hist_off, seg_q_start, seg_slot, C, taps);
     else
         conv_tail_kernel<float><<<grid, 256, 0, stream>>>((const float*)p, ldp, state, state_stride, hist_off, seg_q_start, seg_slot, C, taps);
+    return (int)cudaGetLastError();
+}
+
+
+// h [T, ldh] (C channels read), out [T, C] contiguous in the same type; the history lies at state[slot] + hist_off
+MI_EXPORT int mi_short_conv(const void* h, int ldh, const float* w, const float* bias, float* state, long long state_stride, long long hist_off,
+                            void* out, const int* token_seg, const int* seg_q_start, const int* seg_slot, int T_, int num_segs, int C, int taps,
+                            int residual, int act, int dtype, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    dim3 grid(T_, T_ >= 256 ? 1 : min(8, (C + 255) / 256));
+    if (dtype == MI_BF16)
+        short_conv_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)h, ldh, w, bias, state, state_stride, hist_off, (__nv_bfloat16*)out,
+                                                                    token_seg, seg_q_start, seg_slot, C, taps, residual, act);
+    else
+        short_conv_kernel<float><<<grid, 256, 0, stream>>>((const float*)h, ldh, w, bias, state, state_stride, hist_off, (float*)out, token_seg,
+                                                            seg_q_start, seg_slot, C, taps, residual, act);
+    int err = (int)cudaGetLastError();
+    if (err || taps <= 1) return err;
+    dim3 tgrid(num_segs, (C + 255) / 256);
+    if (dtype == MI_BF16)
+        conv_tail_kernel<__nv_bfloat16><<<tgrid, 256, 0, stream>>>((const __nv_bfloat16*)h, ldh, state, state_stride, hist_off, seg_q_start, seg_slot, C, taps);
+    else
+        conv_tail_kernel<float><<<tgrid, 256, 0, stream>>>((const float*)h, ldh, state, state_stride, hist_off, seg_q_start, seg_slot, C, taps);
+    return (int)cudaGetLastError();
+}
+
+// out [T, ldo] float32 = r | k | u | a u | decay | v (ldo >= 5 H D + H V)
+MI_EXPORT int mi_general_delta_prepare(const void* p, int ldp, const void* w2, const float* w0, const float* a_b, float* out, int ldo, int T_,
+                                       int H, int D, int V, int rank, float decay_scale, float unit_eps, int dtype, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    const int tok = T_ >= 512 ? 8 : 1;
+    const size_t smem = (size_t)tok * (rank + H) * sizeof(float);
+    if (smem > 48 * 1024) return -2;
+    const int HD = H * D;
+    dim3 grid((T_ + tok - 1) / tok, tok == 8 ? 1 : min(16, (HD + 255) / 256));
+#define GO(T, TOK) general_delta_prepare_kernel<T, TOK><<<grid, 256, smem, stream>>>((const T*)p, ldp, (const T*)w2, w0, a_b, out, ldo, T_, H, D, V, rank, \
+                                                                                     decay_scale, unit_eps)
+    if (dtype == MI_BF16) { if (tok == 8) GO(__nv_bfloat16, 8); else GO(__nv_bfloat16, 1); }
+    else { if (tok == 8) GO(float, 8); else GO(float, 1); }
+#undef GO
+    return (int)cudaGetLastError();
+}
+
+MI_EXPORT int mi_general_delta_scan(const float* prep, int ld, float* state, long long state_stride, float* out, const int* seg_q_start,
+                                    const int* seg_slot, int T_, int num_segs, int H, int D, int V, cudaStream_t stream) {
+    const int HD = H * D;
+    ScanLayout L{ld, 0, HD, 5 * HD, 4 * HD, 0, 2 * HD, 3 * HD};
+    return launch_scan<2>(prep, L, nullptr, state, state_stride, out, seg_q_start, seg_slot, T_, num_segs, H, H, D, V, stream);
+}
+
+// p [T, ldp] = q | k | v (| gate, at `gate`); gl float32 [T, 2 H] gate logits; lg [T, 2 H], mneg [T, H], prep [T, ldprep], full [T, H (V + 4)]:
+// float32 scratch.  The slot holds H D (V + 4) state floats, then the H running maxima.  y [T, H V] in the type of p.
+MI_EXPORT int mi_matrix_memory(const void* p, int ldp, const float* gl, const float* gate_bias, float cap, int capped, float den_eps,
+                               const float* norm, const void* gate, int gate_stride, float eps, float* lg, float* mneg, float* prep, int ldprep,
+                               float* full, void* y, float* state, long long state_stride, const int* seg_q_start, const int* seg_slot,
+                               int T_, int num_segs, int H, int D, int V, int dtype, cudaStream_t stream) {
+    if (T_ == 0) return 0;
+    const int W = V + 4, HD = H * D, n = T_ * 2 * H;
+    if (H > 65535) return -2;
+    memory_gates_kernel<<<(n + 255) / 256, 256, 0, stream>>>(gl, gate_bias, lg, n, H, cap, capped);
+    memory_max_kernel<<<num_segs, min(256, (H + 31) / 32 * 32), 0, stream>>>(lg, mneg, state, state_stride, (long long)HD * W, seg_q_start, seg_slot, H);
+    const float q_scale = 1.f / sqrtf((float)D);
+    if (dtype == MI_BF16) memory_prepare_kernel<__nv_bfloat16><<<T_, 256, 0, stream>>>((const __nv_bfloat16*)p, ldp, lg, prep, ldprep, H, D, V, q_scale);
+    else memory_prepare_kernel<float><<<T_, 256, 0, stream>>>((const float*)p, ldp, lg, prep, ldprep, H, D, V, q_scale);
+    int err = (int)cudaGetLastError();
+    if (err) return err;
+    ScanLayout L{ldprep, 0, HD, 2 * HD, 0, 2 * HD + H * W, 0, 0};
+    err = launch_scan<3>(prep, L, nullptr, state, state_stride, full, seg_q_start, seg_slot, T_, num_segs, H, H, D, W, stream);
+    if (err) return err;
+    dim3 grid(T_, H);
+    if (dtype == MI_BF16)
+        memory_output_kernel<__nv_bfloat16><<<grid, 32, 0, stream>>>(full, mneg, norm, (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)y, H, V, den_eps, eps);
+    else
+        memory_output_kernel<float><<<grid, 32, 0, stream>>>(full, mneg, norm, (const float*)gate, gate_stride, (float*)y, H, V, den_eps, eps);
+    return (int)cudaGetLastError();
+}
+
+// x [T, I] and out [T, I] contiguous in the run's type; dt float32 [T, I] (before bias and softplus); B, C, z: strided views; A float32 [I, N]
+MI_EXPORT int mi_selective_scan(const void* x, const float* dt, const float* dt_b, const float* A, const void* B, int ldb, const void* C, int ldc,
+                                const float* Dv, const void* z, int ldz, float* state, long long state_stride, void* out,
+                                const int* seg_q_start, const int* seg_slot, int T_, int num_segs, int I, int N, int dtype, cudaStream_t stream) {
+    if (T_ == 0 || num_segs == 0) return 0;
+    if (N > 128) return -2;
+    const int NG = (N + 7) / 8;
+    const size_t smem = (size_t)SS_TC * (2 * N + 96) * sizeof(float);
+    dim3 grid(num_segs, (I + 31) / 32);
+    if (grid.y > 65535) return -2;
+#define GO(T, G) selective_scan_kernel<T, G><<<grid, 256, smem, stream>>>((const T*)x, dt, dt_b, A, (const T*)B, ldb, (const T*)C, ldc, Dv, (const T*)z, ldz, \
+                                                                          state, state_stride, (T*)out, seg_q_start, seg_slot, I, N)
+#define PICK(T) do { if (NG <= 1) GO(T, 1); else if (NG == 2) GO(T, 2); else if (NG == 3) GO(T, 3); else if (NG == 4) GO(T, 4); \
+                     else if (NG <= 8) GO(T, 8); else GO(T, 16); } while (0)
+    if (dtype == MI_BF16) PICK(__nv_bfloat16); else PICK(float);
+#undef PICK
+#undef GO
     return (int)cudaGetLastError();
 }

@@ -14,6 +14,8 @@ import os
 
 import torch
 
+from ..parts.base import GatedDelta
+
 _LIB = None
 _c = ctypes
 
@@ -799,11 +801,20 @@ class CudaOps:
         return x if rows is None else rows
 
     def stream_rmsnorm(self, x, delta, weight, eps, rows, out_dtype):
-        """x (float32 stream) += delta if given; y = weight * x / rms(x) in out_dtype.  rows: only these rows, stream untouched."""
-        assert x.dtype == torch.float32 and x.is_contiguous() and (delta is None or delta.is_contiguous())
+        """x (float32 stream) += delta if given; y = weight * x / rms(x) in out_dtype.  rows: only these rows, stream untouched.
+        A GatedDelta adds sigmoid(logits + bias) * (y + y_bias) instead, gate and sum in float32, in the same kernel."""
         hidden = x.shape[-1]
         n = x.shape[0] if rows is None else rows.shape[0]
         y = torch.empty((n, hidden), dtype=out_dtype, device=x.device)
+        if isinstance(delta, GatedDelta):
+            d = delta
+            assert x.dtype == torch.float32 and x.is_contiguous() and d.y.is_contiguous() and d.logits.is_contiguous() and d.y.dtype == d.logits.dtype
+            assert d.y.shape == x.shape and d.logits.shape == x.shape and d.bias.dtype == torch.float32
+            _check(self.lib.mi_stream_rmsnorm_gated(_p(x), _p(d.y), _p(d.logits), _p(d.bias), _p(d.y_bias), _p(weight), _p(y), _p(rows), n, hidden,
+                                                    _c.c_float(eps), _code(d.y.dtype), _code(out_dtype), self._stream()), "stream_rmsnorm_gated")
+            self.launches += 1
+            return y
+        assert x.dtype == torch.float32 and x.is_contiguous() and (delta is None or delta.is_contiguous())
         _check(self.lib.mi_stream_rmsnorm(_p(x), _p(delta), _p(weight), _p(y), _p(rows), n, hidden, _c.c_float(eps),
                                           _code(delta.dtype if delta is not None else out_dtype), _code(out_dtype), self._stream()),
                "stream_rmsnorm")
@@ -824,16 +835,23 @@ class CudaOps:
         self.launches += 1
         return p[:, :H * D]
 
-    def masked_attention(self, q, k_cache, v_cache, meta, H, KV, D, V, scale, block_size, window, sink):
+    def masked_attention(self, q, k_cache, v_cache, meta, H, KV, D, V, scale, block_size, window, sink, sink_values=None, distance_bias=None):
         """q [T, H D] (a strided view is allowed) over the pages; keys of D and values of V entries; block_size / window / sink as
-        csrc/attention_masked.cu states them.  Scores, weights and sums are float32.  Returns [T, H V]."""
+        csrc/attention_masked.cu states them.  sink_values float32 [H]: the sink's score per head (None: 0); distance_bias float32
+        [far + 1, H]: added to the scaled score by the distance i - j (beyond far: the last row).  Scores, weights and sums are
+        float32.  Returns [T, H V]."""
         T = q.shape[0]
         assert q.stride(1) == 1
         out = torch.empty((T, H * V), dtype=q.dtype, device=q.device)
         code, blk, win = _code(q.dtype), int(block_size or 0), int(window or 0)
         rows = getattr(meta, "table_rows", None)
         num_decode, num_tiles = meta.decode_segs.shape[0], meta.prefill_tiles.shape[0]
-        if (num_tiles and self.fast_attention and q.dtype == torch.bfloat16 and D == V and D in (64, 128) and meta.tile == 64
+        plain = sink_values is None and distance_bias is None
+        if not plain:
+            assert sink_values is None or (sink and sink_values.dtype == torch.float32 and sink_values.numel() == H)
+            assert distance_bias is None or (distance_bias.dtype == torch.float32 and distance_bias.is_contiguous() and distance_bias.shape[1] == H)
+        bias_last = 0 if distance_bias is None else distance_bias.shape[0] - 1
+        if (num_tiles and plain and self.fast_attention and q.dtype == torch.bfloat16 and D == V and D in (64, 128) and meta.tile == 64
                 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
             # key and value rows of 64 or 128 entries: the mma.sync prompt kernel, every softmax weight entering P V as two
             # bfloat16 numbers (float32 scores and softmax, 16 mantissa bits of each weight, float32 sums)
@@ -846,13 +864,13 @@ class CudaOps:
             _check(self.lib.mi_masked_prefill(
                 _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(meta.prefill_tiles), num_tiles, _p(meta.seg_q_start),
                 _p(meta.seg_pos0), _p(meta.block_table), _p(rows), meta.max_pages, H, KV, D, V, meta.page_size, meta.tile,
-                _c.c_float(scale), blk, win, int(bool(sink)), code, self._stream()), "masked_prefill")
+                _c.c_float(scale), blk, win, int(bool(sink)), _p(sink_values), _p(distance_bias), bias_last, code, self._stream()), "masked_prefill")
             self.launches += 1
         if not num_decode:
             return out
         reach = meta.max_kv_len if not blk else min(meta.max_kv_len, blk)              # the most keys a decoded token can see
         reach = reach if not win else min(reach, win)
-        if (self.fast_attention and q.dtype == torch.bfloat16 and D == V and D in (64, 128) and H // KV <= 16 and meta.page_size % 16 == 0
+        if (plain and self.fast_attention and q.dtype == torch.bfloat16 and D == V and D in (64, 128) and H // KV <= 16 and meta.page_size % 16 == 0
                 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
             # the tensor-core decode kernel (the G query heads of a kv head are the rows of one tile), split weights
             S = self.choose_splits(num_decode * KV, reach, 2 if self.bulk_decode else 3, cluster=self.bulk_decode and self.cluster_merge, head_dim=D)
@@ -885,7 +903,8 @@ class CudaOps:
             _check(self.lib.mi_masked_decode(
                 _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(o_part), _p(lse), _p(meta.decode_segs), num_decode,
                 _p(meta.seg_q_start), _p(meta.seg_kv_len), _p(meta.block_table), _p(rows), meta.max_pages, H, KV, D, V,
-                meta.page_size, S, _c.c_float(scale), blk, win, int(bool(sink)), code, self._stream()), "masked_decode")
+                meta.page_size, S, _c.c_float(scale), blk, win, int(bool(sink)), _p(sink_values), _p(distance_bias), bias_last, code,
+                self._stream()), "masked_decode")
             self.launches += 2 if S > 1 else 1
         return out
 
@@ -907,34 +926,43 @@ class CudaOps:
         return out
 
     # ---------------------------------------------------------------- routed experts
-    def route_topk(self, h, router, correction, top, groups):
-        """(chosen int32 [T, top], weights float32 [T, top]).  router [E, hidden] in the dtype of h, correction float32 [E];
-        groups None or (count, keep).  Products, sums, softmax and the choice are float32 (csrc/moe.cu)."""
-        T, E = h.shape[0], router.shape[0]
-        assert h.stride(1) == 1 and router.dtype == h.dtype and router.is_contiguous() and correction.dtype == torch.float32
+    def route_topk(self, h, router, correction, top, groups, score=None, extra_rows=0):
+        """(chosen int32 [T, top], weights float32 [T, top]).  router [E, hidden] in the dtype of h, correction float32 [E] or None;
+        groups None or (count, keep).  Products, sums, scores and the choice are float32 (csrc/moe.cu).  Called with `score`
+        ("softmax" or "sigmoid") it answers (chosen, weights, extra): the router matrix then has extra_rows more rows behind the
+        experts' and extra float32 [T, extra_rows] holds their logits (None without extra rows)."""
+        T, E = h.shape[0], router.shape[0] - extra_rows
+        assert h.stride(1) == 1 and router.dtype == h.dtype and router.is_contiguous() and (correction is None or correction.dtype == torch.float32)
         chosen = torch.empty((T, top), dtype=torch.int32, device=h.device)
         weights = torch.empty((T, top), dtype=torch.float32, device=h.device)
+        extra = torch.empty((T, extra_rows), dtype=torch.float32, device=h.device) if extra_rows else None
         count, keep = groups if groups else (0, 0)
         _check(self.lib.mi_route_topk(_p(h), h.stride(0), _p(router), _p(correction), _p(chosen), _p(weights), T, h.shape[1], E, top,
-                                      count, keep, _code(h.dtype), self._stream()), "route_topk")
+                                      count, keep, int(score == "sigmoid"), extra_rows, _p(extra), _code(h.dtype), self._stream()), "route_topk")
         self.launches += 1
-        return chosen, weights
+        return (chosen, weights) if score is None else (chosen, weights, extra)
 
     def clamped_glu(self, gu, limit, slope):
         """[g | u] -> min(g, limit) * sigmoid(slope * min(g, limit)) * (clamp(u, -limit, limit) + 1)."""
         rows, inter = gu.shape[0], gu.shape[1] // 2
         assert gu.is_contiguous()
         out = torch.empty((rows, inter), dtype=gu.dtype, device=gu.device)
-        _check(self.lib.mi_clamped_glu(_p(gu), _p(out), rows, inter, _c.c_float(limit), _c.c_float(slope), _code(gu.dtype),
+        _check(self.lib.mi_clamped_glu(_p(gu), _p(out), rows, inter, _c.c_float(limit), _c.c_float(slope), _c.c_float(1.0), _code(gu.dtype),
                                        self._stream()), "clamped_glu")
         self.launches += 1
         return out
 
-    def expert_ffn(self, h, chosen, weights, w_in, w_out, limit, slope, shared):
+    def expert_ffn(self, h, chosen, weights, w_in, w_out, limit, slope, shared, up_shift=1.0, weight_on_input=False, shared_gate=None):
         """sum_j weights[t, j] * expert_{chosen[t, j]}(h[t]) (+ shared[t]).  w_in [E, 2 F, hidden] (gate rows | up rows),
         w_out [E, hidden, F].  The (token, choice) pairs are sorted by expert on the device; two grouped products run over the
-        sorted rows, the first with the clamped gated activation in its epilogue; nothing returns to the host."""
+        sorted rows, the first with the gated activation min(g, limit) sigmoid(slope g) (clamp(u) + up_shift) in its epilogue;
+        nothing returns to the host.  weight_on_input: sum_j expert(weights[t, j] * h[t]) instead (the rows are scaled where they
+        are gathered, the sum is unweighted).  shared_gate float32 [T, 1]: shared[t] is multiplied by sigmoid of it."""
         T, top = chosen.shape
+        sh = _c.c_float(up_shift)
+        sum_weights = None if weight_on_input else weights
+        sg = None if shared_gate is None else shared_gate.reshape(-1)
+        assert sg is None or (sg.dtype == torch.float32 and sg.is_contiguous() and sg.numel() == T and shared is not None)
         E, F2, K = w_in.shape
         F, hidden = F2 // 2, w_out.shape[1]
         assert h.stride(1) == 1 and w_in.is_contiguous() and w_out.is_contiguous() and K == h.shape[1] and w_in.dtype == h.dtype
@@ -948,19 +976,25 @@ class CudaOps:
             tile_expert = torch.empty(cap_tiles, dtype=torch.int32, device=dev)
             _check(self.lib.mi_moe_align(_p(chosen), P, E, 128, _p(sorted_pair), cap_pos, _p(tile_expert), cap_tiles, self._stream()), "moe_align")
             a = torch.empty((cap_pos, K), dtype=h.dtype, device=dev)
-            _check(self.lib.mi_moe_gather_rows(_p(h), h.stride(0), _p(sorted_pair), top, _p(a), cap_pos, K, self._stream()), "moe_gather_rows")
+            _check(self.lib.mi_moe_gather_rows(_p(h), h.stride(0), _p(sorted_pair), top, _p(a), cap_pos, K, _p(weights if weight_on_input else None), self._stream()), "moe_gather_rows")
             y = torch.empty((cap_pos, F), dtype=h.dtype, device=dev)
             rows = torch.empty((P, hidden), dtype=h.dtype, device=dev)
             _check(self.lib.mi_moe_gemm_tcgen05(_p(a), _p(w_in), E, _p(y), F, _p(sorted_pair), _p(tile_expert), cap_tiles, F, K,
-                                                _c.c_float(limit), _c.c_float(slope), 0, _p(self._stream_error), self._stream()), "moe_gemm_tcgen05 (in)")
+                                                _c.c_float(limit), _c.c_float(slope), sh, 0, _p(self._stream_error), self._stream()), "moe_gemm_tcgen05 (in)")
             _check(self.lib.mi_moe_gemm_tcgen05(_p(y), _p(w_out), E, _p(rows), hidden, _p(sorted_pair), _p(tile_expert), cap_tiles, hidden, F,
-                                                _c.c_float(limit), _c.c_float(slope), 1, _p(self._stream_error), self._stream()), "moe_gemm_tcgen05 (out)")
+                                                _c.c_float(limit), _c.c_float(slope), sh, 1, _p(self._stream_error), self._stream()), "moe_gemm_tcgen05 (out)")
             out = torch.empty((T, hidden), dtype=h.dtype, device=dev)
             assert shared is None or (shared.is_contiguous() and shared.shape == out.shape)
-            _check(self.lib.mi_moe_combine(_p(rows), _p(weights), _p(shared), _p(out), T, hidden, top, code, self._stream()), "moe_combine")
+            _check(self.lib.mi_moe_combine(_p(rows), _p(sum_weights), _p(shared), _p(sg), _p(out), T, hidden, top, code, self._stream()), "moe_combine")
             self.launches += 5
             return out
-        tc = h.dtype == torch.bfloat16 and self.moe_tc and K % 64 == 0 and F % 64 == 0 and hidden % 2 == 0 and h.stride(0) % 8 == 0
+        src, src_top = h, top
+        if weight_on_input:                                # row p = weights[p] * h[p // top]; the products then see one choice per row
+            src = torch.empty((P, K), dtype=h.dtype, device=dev)
+            _check(self.lib.mi_moe_scale_rows(_p(h), h.stride(0), _p(weights), top, _p(src), P, K, code, self._stream()), "moe_scale_rows")
+            src_top = 1
+            self.launches += 1
+        tc = h.dtype == torch.bfloat16 and self.moe_tc and K % 64 == 0 and F % 64 == 0 and hidden % 2 == 0 and src.stride(0) % 8 == 0
         BM = int(self.lib.mi_moe_tile_rows_tc(P, E) if tc else self.lib.mi_moe_tile_rows_simt())
         cap_tiles = (P + BM - 1) // BM + min(E, P)
         cap_pos = cap_tiles * BM
@@ -971,14 +1005,133 @@ class CudaOps:
         rows = torch.empty((P, hidden), dtype=h.dtype, device=dev)
         gemm = self.lib.mi_moe_gemm_tc if tc else self.lib.mi_moe_gemm_simt
         extra = (BM,) if tc else ()
-        _check(gemm(_p(h), h.stride(0), _p(w_in), _p(y), F, _p(sorted_pair), _p(tile_expert), cap_tiles, top, F, K,
-                    _c.c_float(limit), _c.c_float(slope), 0, *extra, code, self._stream()), "moe_gemm (in)")
-        _check(gemm(_p(y), F, _p(w_out), _p(rows), hidden, _p(sorted_pair), _p(tile_expert), cap_tiles, top, hidden, F,
-                    _c.c_float(limit), _c.c_float(slope), 1, *extra, code, self._stream()), "moe_gemm (out)")
+        _check(gemm(_p(src), src.stride(0), _p(w_in), _p(y), F, _p(sorted_pair), _p(tile_expert), cap_tiles, src_top, F, K,
+                    _c.c_float(limit), _c.c_float(slope), sh, 0, *extra, code, self._stream()), "moe_gemm (in)")
+        _check(gemm(_p(y), F, _p(w_out), _p(rows), hidden, _p(sorted_pair), _p(tile_expert), cap_tiles, src_top, hidden, F,
+                    _c.c_float(limit), _c.c_float(slope), sh, 1, *extra, code, self._stream()), "moe_gemm (out)")
         out = torch.empty((T, hidden), dtype=h.dtype, device=dev)
         assert shared is None or (shared.is_contiguous() and shared.shape == out.shape)
-        _check(self.lib.mi_moe_combine(_p(rows), _p(weights), _p(shared), _p(out), T, hidden, top, code, self._stream()), "moe_combine")
+        _check(self.lib.mi_moe_combine(_p(rows), _p(sum_weights), _p(shared), _p(sg), _p(out), T, hidden, top, code, self._stream()), "moe_combine")
         self.launches += 4
+        return out
+
+    # ---------------------------------------------------------------- hashed pair embedding, input filter, bias + activation, soft cap
+    def embed_bigram_stream(self, ids, table, pairs, buckets, mul_prev, mul_cur, state, batch):
+        """x float32 [T, hidden] = table[id] + pairs[(prev * mul_prev + id * mul_cur) mod buckets]; a token at position 0 takes row
+        `buckets`.  prev of an entry's first token is what its slot of state (int32 [slots, 1]) remembers; the entry's last token is
+        left there."""
+        T, hidden = ids.shape[0], table.shape[1]
+        assert state.dtype == torch.int32 and state.is_contiguous() and pairs.dtype == table.dtype and pairs.shape == (buckets + 1, hidden)
+        x = torch.empty((T, hidden), dtype=torch.float32, device=table.device)
+        _check(self.lib.mi_embed_pair_stream(_p(ids), _p(table), _p(pairs), _p(x), _p(state), _c.c_longlong(state.stride(0)), _p(batch.positions),
+                                             _p(batch.token_seg), _p(batch.seg_q_start), _p(batch.seg_slot), T, hidden, table.shape[0],
+                                             _c.c_longlong(buckets), _c.c_longlong(mul_prev), _c.c_longlong(mul_cur), _code(table.dtype),
+                                             self._stream()), "embed_bigram_stream")
+        self.launches += 1
+        return x
+
+    def short_conv(self, h, weight, bias, taps, state, offset, batch, residual=False, act="none"):
+        """Causal convolution over time on every channel: out[t] = act(sum_j weight[:, j] h[t - taps + 1 + j] + bias) (+ h[t] when
+        residual).  h [T, C] may be a strided view; weight float32 [C, taps]; the inputs before an entry's first token are read from
+        state[slot, offset : offset + (taps - 1) C] (float32), which then receives the entry's last taps - 1 inputs."""
+        T, C = h.shape
+        assert h.stride(1) == 1 and weight.dtype == torch.float32 and weight.is_contiguous() and weight.shape == (C, taps)
+        assert state is None or (state.dtype == torch.float32 and state.is_contiguous())
+        assert taps == 1 or state is not None
+        out = torch.empty((T, C), dtype=h.dtype, device=h.device)
+        _check(self.lib.mi_short_conv(_p(h), h.stride(0), _p(weight), _p(bias), _p(state), _c.c_longlong(state.stride(0) if state is not None else 0),
+                                      _c.c_longlong(offset), _p(out), _p(batch.token_seg), _p(batch.seg_q_start), _p(batch.seg_slot), T,
+                                      batch.num_segs, C, taps, int(residual), {"none": 0, "silu": 1}[act], _code(h.dtype), self._stream()),
+               "short_conv")
+        self.launches += 2 if taps > 1 else 1
+        return out
+
+    def bias_act(self, z, bias, act):
+        """z + bias (float32 [cols]), then act: "none" or "relu2" (the square of relu)."""
+        assert z.is_contiguous() and bias.dtype == torch.float32 and bias.numel() == z.shape[-1]
+        out = torch.empty_like(z)
+        _check(self.lib.mi_bias_act(_p(z), _p(bias), _p(out), _c.c_longlong(z.numel() // z.shape[-1]), z.shape[-1], {"none": 0, "relu2": 1}[act],
+                                    _code(z.dtype), self._stream()), "bias_act")
+        self.launches += 1
+        return out
+
+    def softcap(self, logits, cap):
+        """logits <- cap * tanh(logits / cap), in place (float32)."""
+        assert logits.dtype == torch.float32 and logits.is_contiguous()
+        _check(self.lib.mi_softcap(_p(logits), _c.c_longlong(logits.numel()), _c.c_float(cap), self._stream()), "softcap")
+        self.launches += 1
+        return logits
+
+    def dual_rmsnorm_mix(self, a, wa, sa, b, wb, sb, eps):
+        """sa * wa * a / rms(a) + sb * wb * b / rms(b) over the rows of a and b (same shape and dtype), float32 statistics."""
+        assert a.is_contiguous() and b.is_contiguous() and a.shape == b.shape and a.dtype == b.dtype
+        out = torch.empty_like(a)
+        _check(self.lib.mi_dual_rmsnorm_mix(_p(a), _p(wa), _c.c_float(sa), _p(b), _p(wb), _c.c_float(sb), _p(out), a.shape[0], a.shape[1],
+                                            _c.c_float(eps), _code(a.dtype), self._stream()), "dual_rmsnorm_mix")
+        self.launches += 1
+        return out
+
+    # ---------------------------------------------------------------- three more recurrences
+    def general_delta_prepare(self, p, w2, w0, a_b, H, D, V, rank, decay_scale, unit_eps):
+        """p [T, 3 H D + 2 H V + rank] = r | k | v | a | g | low.  Returns float32 [T, 5 H D + H V (padded to four)] =
+        r | k | u | a u | decay | v with u = k / sqrt(sum k^2 + unit_eps) per head, a = sigmoid(. + a_b),
+        decay = exp(-decay_scale * sigmoid(w2 tanh(low) + w0))."""
+        T = p.shape[0]
+        assert p.stride(1) == 1 and w2.is_contiguous() and w2.dtype == p.dtype and w2.shape == (H * D, rank)
+        out = torch.empty((T, (5 * H * D + H * V + 3) // 4 * 4), dtype=torch.float32, device=p.device)
+        _check(self.lib.mi_general_delta_prepare(_p(p), p.stride(0), _p(w2), _p(w0), _p(a_b), _p(out), out.stride(0), T, H, D, V, rank,
+                                                 _c.c_float(decay_scale), _c.c_float(unit_eps), _code(p.dtype), self._stream()),
+               "general_delta_prepare")
+        self.launches += 1
+        return out
+
+    def general_delta_scan(self, prep, H, D, V, state, batch):
+        """S <- diag(decay) S - (a u)(u^T S) + k v^T, both terms reading the old S; o = S^T r.  float32 [T, H V]."""
+        T = prep.shape[0]
+        assert prep.dtype == torch.float32 and state.dtype == torch.float32 and state.is_contiguous()
+        out = torch.empty((T, H * V), dtype=torch.float32, device=prep.device)
+        _check(self.lib.mi_general_delta_scan(_p(prep), prep.stride(0), _p(state), _c.c_longlong(state.stride(0)), _p(out), _p(batch.seg_q_start),
+                                              _p(batch.seg_slot), T, batch.num_segs, H, D, V, self._stream()), "general_delta_scan")
+        self.launches += 1
+        return out
+
+    def matrix_memory(self, p, gl, gate_bias, H, D, V, cap, den_eps, norm, gate, eps, state, batch, out_dtype):
+        """p [T, >= 2 H D + H V] = q | k | v; gl float32 [T, 2 H] = logits of the input and forget gates; the slot holds per head
+        [D, V + 4] floats (memory, normaliser column, three unused) and behind them the H running maxima.  Returns the rows
+        o / rms(o) * norm * sigmoid(gate) per head in out_dtype (gate [T, H V] may be a strided view)."""
+        T = p.shape[0]
+        W = V + 4
+        assert p.stride(1) == 1 and gate.stride(1) == 1 and gate.dtype == p.dtype == out_dtype and gl.dtype == torch.float32 and gl.is_contiguous()
+        assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] >= H * D * W + H
+        dev = p.device
+        lg = torch.empty((T, 2 * H), dtype=torch.float32, device=dev)
+        mneg = torch.empty((T, H), dtype=torch.float32, device=dev)
+        prep = torch.empty((T, (2 * H * D + H * W + H + 3) // 4 * 4), dtype=torch.float32, device=dev)
+        full = torch.empty((T, H * W), dtype=torch.float32, device=dev)
+        y = torch.empty((T, H * V), dtype=out_dtype, device=dev)
+        _check(self.lib.mi_matrix_memory(_p(p), p.stride(0), _p(gl), _p(gate_bias), _c.c_float(cap or 0.0), int(cap is not None), _c.c_float(den_eps),
+                                         _p(norm), _p(gate), gate.stride(0), _c.c_float(eps), _p(lg), _p(mneg), _p(prep), prep.stride(0), _p(full),
+                                         _p(y), _p(state), _c.c_longlong(state.stride(0)), _p(batch.seg_q_start), _p(batch.seg_slot), T,
+                                         batch.num_segs, H, D, V, _code(p.dtype), self._stream()), "matrix_memory")
+        self.launches += 5
+        return y
+
+    def selective_scan(self, x, dt, dt_b, A, B, C, Dv, z, state, batch, out_dtype):
+        """S[c, n] <- exp(step_c A[c, n]) S[c, n] + step_c x_c B_n, step = softplus(dt + dt_b); y_c = sum_n S[c, n] C_n + Dv_c x_c;
+        returns y * silu(z) in out_dtype.  x [T, I] contiguous; dt [T, I] in the run's dtype or float32; B, C [T, N] and z [T, I] may be
+        strided views; A float32 [I, N]; the slot's first I N floats are S."""
+        T, I = x.shape
+        N = A.shape[1]
+        assert x.is_contiguous() and x.dtype == out_dtype and B.stride(1) == 1 and C.stride(1) == 1 and z.stride(1) == 1
+        assert A.dtype == torch.float32 and A.is_contiguous() and state.dtype == torch.float32 and state.is_contiguous()
+        if dt.dtype != torch.float32:
+            dt = dt.float()
+        assert dt.is_contiguous()
+        out = torch.empty((T, I), dtype=out_dtype, device=x.device)
+        _check(self.lib.mi_selective_scan(_p(x), _p(dt), _p(dt_b), _p(A), _p(B), B.stride(0), _p(C), C.stride(0), _p(Dv), _p(z), z.stride(0),
+                                          _p(state), _c.c_longlong(state.stride(0)), _p(out), _p(batch.seg_q_start), _p(batch.seg_slot), T,
+                                          batch.num_segs, I, N, _code(x.dtype), self._stream()), "selective_scan")
+        self.launches += 1
         return out
 
     # ---------------------------------------------------------------- sampling

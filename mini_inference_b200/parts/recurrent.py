@@ -344,6 +344,6 @@ class SelectiveScan(Part):
         xz = ops.linear(h, self.w_in)                               # [T, 2 I]: x | z
         x = ops.short_conv(xz[:, :I], self.conv, self.conv_b, self.taps, cache.state, I * N, ctx.batch, residual=False, act="silu")
         p = ops.linear(x, self.w_x)                                 # [T, R + 2 N]: dt_low | B | C
-        dt = ops.linear(p[:, :R], self.w_dt)                        # [T, I], before bias and softplus
+        dt = ops.linear(p[:, :R], self.w_dt, out_dtype=torch.float32)    # [T, I] float32, before bias and softplus
         y = ops.selective_scan(x, dt, self.dt_b, self.A, p[:, R:R + N], p[:, R + N:], self.Dv, xz[:, I:], cache.state, ctx.batch, ctx.dtype)
         return ops.linear(y, self.o)
