@@ -219,8 +219,11 @@ def check_mixed(make, d, vocab, page, tol, lens=(23, 9, 31, 17, 40, 12, 27, 36, 
         for k in [k for k, (seq, at) in live.items() if at == len(reqs[k])]:
             runner.cache.free(live.pop(k)[0])
         runner.cache.check_invariants()
-    for k in reqs:
-        assert_close(torch.cat(got[k]), want[k], tol, k)
+    if tol < 1e-2:
+        for k in reqs:
+            assert_close(torch.cat(got[k]), want[k], tol, k)
+    else:                                                        # bfloat16: the positions of all requests judged together (see assert_close)
+        assert_close(torch.cat([torch.cat(got[k]) for k in reqs]), torch.cat([want[k] for k in reqs]), tol, "all requests")
     assert runner.cache.free_pages() == pages
     assert len(slot_uses) <= 4 and max(slot_uses.values()) >= 2, "no state slot was used again"
     assert sum(n - 1 for n in takes.values()) * 3 >= sum(takes.values()), "too few pages were used again"
@@ -471,3 +474,424 @@ def test_trace_replay_in_process(dirs, tmp_path, monkeypatch, capsys):
     g1 = torch.from_numpy(np.fromfile(os.path.join(tmp_path, "1.f32"), dtype="<f4").reshape(3, -1))
     g2 = torch.from_numpy(np.fromfile(os.path.join(tmp_path, "2.f32"), dtype="<f4").reshape(1, -1))
     assert err(g0, wa[4:5]) < 2e-5 and err(g1, torch.stack([wb[2], wb[5], wa[5]])) < 2e-5 and err(g2, wa[8:9]) < 2e-5
+
+
+# ---------------------------------------------------------------- inputs made so that a fault shows
+def _i32(v, device):
+    return torch.tensor(v, dtype=torch.int32, device=device)
+
+
+def biased_key_case(ops, device, dtype, L, hot, window, page, rows=1, H=4, KV=2, D=24, V=16, table_rows=8, far=40):
+    """L cached keys over shuffled pages; the entry feeds the last `rows` positions and the LAST query is looked at.  Every key
+    is orthogonal to the query except key `hot`, whose scaled score stands out by 30.  A key that the query may see wins the
+    softmax against the distance table and the sink; if `hot` lies outside the window, the visible scores are the distance
+    table's entries alone and the output is sum_j e^{b_j} v_j / (sum_j e^{b_j} + e^{sink})."""
+    g = torch.Generator().manual_seed(L * 1000 + hot)
+    keys, vals = torch.randn(L, KV, D, generator=g) * 0.3, torch.randn(L, KV, V, generator=g)
+    target = torch.randn(D, generator=g)
+    target = target / target.norm()
+    keys -= (keys @ target)[..., None] * target
+    keys[hot] += 6.0 * target
+    rel, sink = torch.randn(table_rows, H, generator=g), torch.randn(H, generator=g)
+    by_distance = torch.stack([rel[plain.distance_bucket(n, table_rows, far)] for n in range(far + 1)])
+    pages = -(-L // page)
+    order = torch.randperm(pages, generator=g) + 1               # page 0 is the null page
+    kc, vc = torch.zeros(pages + 1, KV, page, D), torch.zeros(pages + 1, KV, page, V)
+    for j in range(L):
+        kc[order[j // page], :, j % page], vc[order[j // page], :, j % page] = keys[j], vals[j]
+    table = torch.zeros(2, pages, dtype=torch.int32)
+    table[1] = order.to(torch.int32)
+    tiles = [(0, r) for r in range(0, rows, 64)] if rows > 1 else []
+    meta = SimpleNamespace(seg_q_start=_i32([0, rows], device), seg_pos0=_i32([L - rows], device), seg_kv_len=_i32([L], device),
+                           table_rows=_i32([1], device), block_table=table.to(device), max_pages=pages, page_size=page,
+                           decode_segs=_i32([0] if rows == 1 else [], device), prefill_tiles=_i32(tiles, device).view(-1, 2), tile=64, max_kv_len=L)
+    q = torch.randn(rows, H, D, generator=g)
+    q[-1] = 10.0 * target                                        # times the scale of 0.5: 5, times the key's 6: a score of 30
+    out = ops.masked_attention(q.reshape(rows, H * D).to(device, dtype), kc.to(device, dtype), vc.to(device, dtype), meta, H, KV, D, V, 0.5,
+                               None, window, True, sink_values=sink.to(device), distance_bias=by_distance.to(device)).float().cpu()[-1].view(H, V)
+    p = L - 1
+    lo = 0 if not window else max(0, p - window + 1)
+    kvh = torch.arange(H) // (H // KV)
+    if hot >= lo:
+        return out, vals[hot][kvh], 2e-3                         # what is left for the others: e^{-30 + a few}
+    b = torch.stack([rel[plain.distance_bucket(p - j, table_rows, far)] for j in range(lo, L)])      # [n, H]
+    e = torch.exp(b)
+    want = torch.einsum("jh,jhv->hv", e, vals[lo:][:, kvh]) / (e.sum(0) + torch.exp(sink))[:, None]
+    return out, want, 1e-4
+
+
+# (keys, the hot key, window): the first and last key inside the window and the one just outside, in the middle of a page and at a
+# page's border; windows of one page, of two, of one key; no window with the key far back and at the very start; short sequences
+BIASED = [(300, 0, None), (300, 299, None), (200, 104, 96), (200, 103, 96), (129, 113, 16), (129, 112, 16), (128, 96, 32), (128, 95, 32),
+          (77, 76, 1), (77, 75, 1), (50, 3, 47), (50, 2, 47), (5, 0, 9), (3, 1, 2), (3, 0, 2), (1, 0, 4)]
+
+
+@pytest.mark.parametrize("L,hot,window", BIASED)
+@pytest.mark.parametrize("rows", [1, 3])
+def test_keys_at_window_edges_with_distance_rows_and_sink_on_cpu(L, hot, window, rows):
+    out, want, tol = biased_key_case(TorchRefOps(), "cpu", torch.float32, L, hot, window, page=16, rows=min(rows, L))
+    assert (out - want).abs().max() < tol * want.abs().max() + 1e-6
+
+
+def test_the_learned_sink_counts_once_and_unscaled():
+    """One visible key with score s beside a sink of value c: the weight is e^s / (e^s + e^c) whatever the scale."""
+    ops = TorchRefOps()
+    k, v = torch.zeros(2, 1, 4, 2), torch.zeros(2, 1, 4, 3)
+    k[1, 0, 0], v[1, 0, 0] = torch.tensor([1.0, 0.0]), torch.tensor([1.0, 2.0, 3.0])
+    meta = SimpleNamespace(seg_q_start=_i32([0, 1], "cpu"), seg_pos0=_i32([0], "cpu"), seg_kv_len=_i32([1], "cpu"), table_rows=_i32([0], "cpu"),
+                           block_table=_i32([[1]], "cpu"), max_pages=1, page_size=4, decode_segs=_i32([0], "cpu"),
+                           prefill_tiles=_i32([], "cpu").view(-1, 2), tile=64, max_kv_len=1)
+    for scale in (1.0, 0.25):
+        out = ops.masked_attention(torch.tensor([[2.0, 5.0]]), k, v, meta, 1, 1, 2, 3, scale, None, None, True,
+                                   sink_values=torch.tensor([0.7]), distance_bias=torch.tensor([[0.3], [9.0]]))
+        s = 2.0 * scale + 0.3
+        assert torch.allclose(out[0], v[1, 0, 0] * math.exp(s) / (math.exp(s) + math.exp(0.7)), rtol=1e-5)
+
+
+def _segs(device, cuts_at, n, slot=1):
+    return SimpleNamespace(host={"seg_q_start": [0, n], "seg_slot": [slot]}, num_segs=1, seg_q_start=_i32([0, n], device), seg_slot=_i32([slot], device),
+                           positions=_i32(list(range(cuts_at, cuts_at + n)), device), token_seg=_i32([0] * n, device))
+
+
+CUTS = ([401], [400, 1], [200, 150, 50, 1], [1] * 3 + [398])
+
+
+def far_delta_case(ops, device):
+    """Head 0 decays by 0.999 a token and must still hold a write from 400 tokens back (0.999^400 = 0.67); head 1 decays by 0.5
+    and must not.  Head 2 holds it without decay until token 200 removes the key's direction with rate 1, head 3 until a removal
+    along ANOTHER direction, which must leave it alone.  Whole, with the reader decoded alone, in portions, and after single tokens."""
+    H, D, V, T = 4, 4, 5, 401
+    HD = H * D
+    prep = torch.zeros(T, 5 * HD + H * V)
+    r, k, u, au, d = (prep[:, i * HD:(i + 1) * HD].view(T, H, D) for i in range(5))
+    v = prep[:, 5 * HD:].view(T, H, V)
+    d[:] = 1.0
+    d[:, 0], d[:, 1] = 0.999, 0.5
+    k[0, :, 0], v[0] = 2.0, 3.0                                   # token 0 writes key 2 e_0 with value 3
+    u[200, 2, 0] = au[200, 2, 0] = 1.0                            # head 2: u = e_0, removal 1
+    u[200, 3, 1] = au[200, 3, 1] = 1.0                            # head 3: u = e_1
+    r[T - 1, :, 0] = 1.0                                          # the last token reads along e_0
+    want = torch.tensor([6.0 * 0.999 ** 400, 0.0, 0.0, 6.0])
+    for cuts in CUTS:
+        state = torch.zeros(2, HD * V, device=device)
+        outs, at = [], 0
+        for n in cuts:
+            outs.append(ops.general_delta_scan(prep[at:at + n].contiguous().to(device), H, D, V, state, _segs(device, at, n)).cpu())
+            at += n
+        o = torch.cat(outs)[T - 1].view(H, V)
+        assert torch.allclose(o, want[:, None].expand(H, V), rtol=2e-4, atol=1e-30), (cuts, o[:, 0])
+
+
+def far_memory_case(ops, device, dtype=torch.float32):
+    """The matrix memory: token 0 writes with an open input gate (+cap), every later token with a closed one (-cap), and the
+    forget gate stays open (log sigmoid(cap) = -e^{-cap}); 400 tokens later the read-out along the first key is still the first
+    value's direction, which the per-head norm turns into v / rms(v).  Head 1's forget gate is closed (-cap): it holds only the
+    latest writes, so its read-out is the LAST value's direction."""
+    H, D, V, T, cap = 2, 4, 6, 401, 8.0
+    g = torch.Generator().manual_seed(5)
+    p = torch.zeros(T, 2 * H * D + H * V)
+    q, k, v = p[:, :H * D].view(T, H, D), p[:, H * D:2 * H * D].view(T, H, D), p[:, 2 * H * D:].view(T, H, V)
+    v[:] = torch.randn(T, H, V, generator=g)
+    k[:, :, 1] = 1.0                                              # later tokens write along e_1 ...
+    k[0], k[0, :, 0] = 0.0, 1.0                                   # ... the first along e_0
+    k[T - 1, 1], k[T - 1, 1, 0] = 0.0, 1.0                        # head 1's last token writes along e_0 too and reads it back
+    q[T - 1, :, 0] = 2.0
+    gl = torch.zeros(T, 2 * H)
+    gl[:, :H] = -100.0                                            # input gates: -cap after the soft cap ...
+    gl[0, :H] = 100.0                                             # ... +cap at the first token
+    gl[T - 1, 1] = 100.0
+    gl[:, H], gl[:, H + 1] = 100.0, -100.0                        # forget gates: head 0 open, head 1 closed
+    want = torch.stack([v[0, 0] / v[0, 0].pow(2).mean().sqrt(), v[T - 1, 1] / v[T - 1, 1].pow(2).mean().sqrt()])
+    norm, gate = torch.ones(H * V), torch.full((T, H * V), 30.0)
+    for cuts in CUTS:
+        state = torch.zeros(2, H * D * (V + 4) + H, device=device)
+        outs, at = [], 0
+        for n in cuts:
+            outs.append(ops.matrix_memory(p[at:at + n].contiguous().to(device, dtype), gl[at:at + n].contiguous().to(device), torch.zeros(2 * H, device=device),
+                                          H, D, V, cap, 1e-6, norm.to(device), gate[at:at + n].contiguous().to(device, dtype), 0.0, state,
+                                          _segs(device, at, n), dtype).float().cpu())
+            at += n
+        o = torch.cat(outs)[T - 1].view(H, V)
+        assert torch.allclose(o, want, rtol=1e-3 if dtype == torch.float32 else 2e-2, atol=1e-3 if dtype == torch.float32 else 2e-2), (cuts, o, want)
+
+
+def far_scan_case(ops, device):
+    """Selective scan: channel 0 (A = -0.001) must still hold a write from 400 tokens back, channel 1 (A = -1) must not; the
+    read-out is step x B C e^{400 step A} silu(z) with step = softplus(dt + bias)."""
+    I, N, T = 2, 3, 401
+    x, B, C = torch.zeros(T, I), torch.zeros(T, N), torch.zeros(T, N)
+    x[0], B[0, 2], C[T - 1, 2] = 1.5, 2.0, 0.5
+    dt, dt_b, z = torch.full((T, I), 0.2), torch.tensor([0.1, 0.1]), torch.ones(T, I)
+    A, Dv = torch.tensor([[-0.001] * N, [-1.0] * N]), torch.tensor([7.0, 7.0])
+    step = math.log1p(math.exp(0.3))
+    silu1 = 1.0 / (1.0 + math.exp(-1.0))
+    want = torch.tensor([step * 1.5 * 2.0 * 0.5 * math.exp(-0.001 * step * 400) * silu1, 0.0])
+    for cuts in CUTS:
+        state = torch.zeros(2, I * N, device=device)
+        outs, at = [], 0
+        for n in cuts:
+            sl = slice(at, at + n)
+            outs.append(ops.selective_scan(x[sl].contiguous().to(device), dt[sl].contiguous().to(device), dt_b.to(device), A.to(device), B[sl].contiguous().to(device),
+                                           C[sl].contiguous().to(device), Dv.to(device), z[sl].contiguous().to(device), state, _segs(device, at, n),
+                                           torch.float32).cpu())
+            at += n
+        o = torch.cat(outs)
+        assert torch.allclose(o[T - 1], want, rtol=2e-4, atol=1e-30), (cuts, o[T - 1])
+        assert torch.allclose(o[0], torch.tensor([(step * 1.5 * 0 + 7.0 * 1.5) * silu1] * 2), rtol=1e-5)      # C is zero there: the skip term alone
+
+
+def test_recurrences_remember_a_far_token_on_cpu():
+    far_delta_case(TorchRefOps(), "cpu")
+    far_memory_case(TorchRefOps(), "cpu")
+    far_scan_case(TorchRefOps(), "cpu")
+
+
+def test_the_pair_table_reads_across_a_portions_start():
+    """The row of the pair table depends on the token BEFORE a portion's first one: two prompts that differ only there must differ
+    at the next position and the filters must carry the difference taps - 1 positions further, also when the portion starts there."""
+    ops = TorchRefOps()
+    table, pairs = torch.zeros(10, 1), torch.arange(8.0).view(8, 1)
+    state = torch.zeros(3, 1, dtype=torch.int32)
+    first = ops.embed_bigram_stream(_i32([4, 1], "cpu"), table, pairs, 7, 3, 2, state, _segs("cpu", 0, 2, slot=2))
+    nxt = ops.embed_bigram_stream(_i32([3], "cpu"), table, pairs, 7, 3, 2, state, _segs("cpu", 2, 1, slot=2))
+    assert first.flatten().tolist() == [7.0, (4 * 3 + 1 * 2) % 7] and nxt.item() == (1 * 3 + 3 * 2) % 7 and state[2, 0].item() == 3
+    # large multipliers and ids: the row is computed in 64 bits
+    big = ops.embed_bigram_stream(_i32([9, 9], "cpu"), table, torch.arange(1022.0).view(1022, 1), 1021, 2 ** 31 - 1, 2 ** 30 + 7, state, _segs("cpu", 5, 2, slot=1))
+    assert big.flatten().tolist() == [float((0 * (2 ** 31 - 1) + 9 * (2 ** 30 + 7)) % 1021), float((9 * (2 ** 31 - 1) + 9 * (2 ** 30 + 7)) % 1021)]
+
+
+# ================================================================ on the GPU
+TOL = {"float32": 1e-4, "bfloat16": 6e-2}
+
+
+def cuda_ops():
+    from mini_inference_b200.ops import get_ops
+    return get_ops("cuda:0")
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_cuts_on_gpu(dirs, name, dtype):
+    d, cfg, page = dirs[name]
+    check_cuts(engine(d, page, 32, dtype, "cuda:0"), d, cfg["vocab"], TOL[dtype])
+    cuda_ops().check_errors()
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["mix", "pages"])
+def test_mixed_batches_on_gpu(dirs, name, dtype):
+    d, cfg, page = dirs[name]
+    check_mixed(lambda pages: engine(d, page, pages, dtype, "cuda:0"), d, cfg["vocab"], page, TOL[dtype])
+    cuda_ops().check_errors()
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(SINGLE))
+def test_each_mechanism_alone_on_gpu(tmp_path, name, dtype):
+    cfg = SINGLE[name]
+    d = single_dir(tmp_path, name)
+    ids = tokens(cfg["vocab"], 150, seed=1)
+    want = plain_logits(d, ids)
+    runner = engine(d, 16, 16, dtype, "cuda:0")
+    assert_close(feed(runner, "w", ids, [150]), want, TOL[dtype], "whole")
+    assert_close(feed(runner, "d", ids, [110] + [1] * 40), want, TOL[dtype], "decode")
+    assert_close(feed(runner, "p", ids, [2, 64, 3, 17, 2, 33, 29]), want, TOL[dtype], "portions")
+    cuda_ops().check_errors()
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("L,hot,window", BIASED + [(1500, 7, None), (1500, 476, 1024), (1500, 475, 1024), (1100, 1030, 70), (1100, 1029, 70)])
+def test_keys_at_window_edges_with_distance_rows_and_sink_on_gpu(L, hot, window, dtype):
+    ops = cuda_ops()
+    for D, V in ((24, 16), (64, 64), (40, 72), (128, 128)):
+        for rows in (1, 3, 70):
+            for splits in (None, 3):
+                ops.force_splits = splits
+                try:
+                    out, want, tol = biased_key_case(ops, "cuda:0", dtype, L, hot, window, page=16, rows=min(rows, L), D=D, V=V)
+                finally:
+                    ops.force_splits = None
+                assert (out - want).abs().max() < (tol if dtype == torch.float32 else 2e-2) * want.abs().max() + 1e-6, (D, V, rows, splits)
+    ops.check_errors()
+
+
+@gpu
+def test_recurrences_remember_a_far_token_on_gpu():
+    far_delta_case(cuda_ops(), "cuda:0")
+    far_memory_case(cuda_ops(), "cuda:0")
+    far_memory_case(cuda_ops(), "cuda:0", torch.bfloat16)
+    far_scan_case(cuda_ops(), "cuda:0")
+    cuda_ops().check_errors()
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_kernels_against_the_stand_ins(dtype):
+    """Every kernel of the design alone, at sizes no model above has (odd ones too), several entries of unequal length in one
+    launch, states that start non-zero and slots out of order, against the plain PyTorch statement of the same op."""
+    from mini_inference_b200.parts.base import GatedDelta
+    ops, ref, dev = cuda_ops(), TorchRefOps(), "cuda:0"
+    g = torch.Generator().manual_seed(0)
+    tol = 3e-5 if dtype == torch.float32 else 2e-2
+    rnd = lambda *s: torch.randn(*s, generator=g).to(dtype)      # noqa: E731
+    f32 = lambda *s: torch.randn(*s, generator=g)                # noqa: E731
+    close = lambda a, b, t=tol: (a.float().cpu() - b.float().cpu()).abs().max() <= t * max(1.0, b.float().abs().max().item())  # noqa: E731
+    lens, slots, qs, T = [1, 23, 6, 2], [3, 1, 4, 2], [0, 1, 24, 30, 32], 32
+    pos = [40] + list(range(0, 23)) + list(range(100, 106)) + [0, 1]
+    seg = [0] + [1] * 23 + [2] * 6 + [3] * 2
+    batch = SimpleNamespace(host={"seg_q_start": qs, "seg_slot": slots}, num_segs=4, positions=_i32(pos, "cpu"), token_seg=_i32(seg, "cpu"),
+                            seg_q_start=_i32(qs, "cpu"), seg_slot=_i32(slots, "cpu"))
+    dbatch = SimpleNamespace(num_segs=4, positions=_i32(pos, dev), token_seg=_i32(seg, dev), seg_q_start=_i32(qs, dev), seg_slot=_i32(slots, dev))
+    # pair embedding: the previous token of an entry comes from its slot; position 0 takes the last row
+    for hid, buckets, mp, mc in ((77, 13, 5, 3), (192, 1, 7, 2), (40, 509, 2 ** 31 - 1, 2 ** 29 + 3)):
+        ids, table, pairs = torch.randint(0, 50, (T,), generator=g, dtype=torch.int32), rnd(50, hid), rnd(buckets + 1, hid)
+        st = torch.randint(0, 50, (5, 1), generator=g, dtype=torch.int32)
+        sa, sb = st.clone().to(dev), st.clone()
+        xa = ops.embed_bigram_stream(ids.to(dev), table.to(dev), pairs.to(dev), buckets, mp, mc, sa, dbatch)
+        assert close(xa, ref.embed_bigram_stream(ids, table, pairs, buckets, mp, mc, sb, batch), 1e-6) and torch.equal(sa.cpu(), sb)
+    # gated addition + norm in one kernel, with and without the addend's bias, on chosen rows too
+    for hid in (77, 192, 1030):
+        x, y, lg, b, yb, w = f32(T, hid), rnd(T, hid), rnd(T, hid), f32(hid), f32(hid), f32(hid)
+        for y_bias in (None, yb):
+            xa, xb = x.clone().to(dev), x.clone()
+            ra = ops.stream_rmsnorm(xa, GatedDelta(y.to(dev), lg.to(dev), b.to(dev), None if y_bias is None else y_bias.to(dev)), w.to(dev), 1e-5, None, dtype)
+            rb = ref.stream_rmsnorm(xb, GatedDelta(y, lg, b, y_bias), w, 1e-5, None, dtype)
+            assert close(xa, xb, 2e-6) and close(ra, rb)
+        a, b2, wa, wb = rnd(T, hid), rnd(T, hid), f32(hid), f32(hid)
+        assert close(ops.dual_rmsnorm_mix(a.to(dev), wa.to(dev), 0.5, b2.to(dev), wb.to(dev), 0.25, 1e-5),
+                     ref.dual_rmsnorm_mix(a, wa, 0.5, b2, wb, 0.25, 1e-5))
+        z = rnd(T, hid)
+        for act in ("none", "relu2"):
+            assert close(ops.bias_act(z.to(dev), b.to(dev), act), ref.bias_act(z, b, act))
+    lo = f32(7, 131) * 40
+    assert close(ops.softcap(lo.clone().to(dev), 25.0), ref.softcap(lo, 25.0), 1e-6)
+    # the filter: one to five taps, a strided view as input, the state behind an offset, with and without bias, activation, residual
+    for C, taps, off in ((48, 4, 0), (77, 2, 5), (192, 3, 192 * 7), (33, 5, 1), (20, 1, 0)):
+        wide, w, b = rnd(T, C + 9), f32(C, taps), f32(C)
+        st = f32(5, off + (taps - 1) * C + 3)
+        for bias, residual, act in ((None, True, "none"), (b, False, "silu"), (b, True, "none")):
+            sa, sb = st.clone().to(dev), st.clone()
+            ya = ops.short_conv(wide.to(dev)[:, 4:4 + C], w.to(dev), None if bias is None else bias.to(dev), taps, sa, off, dbatch, residual, act)
+            yb = ref.short_conv(wide[:, 4:4 + C], w, bias, taps, sb, off, batch, residual, act)
+            assert close(ya, yb) and close(sa, sb, 1e-6), (C, taps)
+    # the general delta rule
+    for H, D, V, rank in ((3, 8, 8, 5), (1, 20, 20, 1), (2, 64, 64, 16), (3, 5, 5, 2), (2, 33, 33, 7), (1, 128, 128, 32)):
+        HD = H * D
+        p, w2, w0, ab = rnd(T, 3 * HD + 2 * H * V + rank + 5), rnd(HD, rank), f32(HD), f32(HD)
+        pa = ops.general_delta_prepare(p.to(dev), w2.to(dev), w0.to(dev), ab.to(dev), H, D, V, rank, 0.6, 1e-6)
+        pb = ref.general_delta_prepare(p, w2, w0, ab, H, D, V, rank, 0.6, 1e-6)
+        assert close(pa[:, :pb.shape[1]], pb, 1e-5 if dtype == torch.float32 else tol)
+        st = f32(5, HD * V + 2) * 0.3
+        sa, sb = st.clone().to(dev), st.clone()
+        oa = ops.general_delta_scan(pa, H, D, V, sa, dbatch)
+        ob = ref.general_delta_scan(pa.cpu()[:, :pb.shape[1]], H, D, V, sb, batch)
+        assert close(oa, ob, 1e-4) and close(sa, sb, 1e-4), (H, D)
+    # the matrix memory, with and without the gates' cap
+    for H, D, V, cap in ((2, 12, 8, 9.0), (1, 16, 20, 2.0), (4, 48, 48, 12.0), (3, 5, 7, None), (2, 64, 128, 15.0), (1, 128, 64, 30.0)):
+        p, gl, gb = rnd(T, 2 * H * D + H * V + 3), f32(T, 2 * H) * 3, f32(2 * H)
+        norm, gate = f32(H * V), rnd(T, H * V + 6)
+        st = torch.zeros(5, H * D * (V + 4) + H)
+        st[:, :H * D * (V + 4)] = f32(5, H * D * (V + 4)) * 0.2
+        st[:, H * D * (V + 4):] = torch.rand(5, H, generator=g) * 2
+        sa, sb = st.clone().to(dev), st.clone()
+        ya = ops.matrix_memory(p.to(dev), gl.to(dev), gb.to(dev), H, D, V, cap, 1e-6, norm.to(dev), gate.to(dev)[:, 3:3 + H * V], 1e-5, sa, dbatch, dtype)
+        yb = ref.matrix_memory(p, gl, gb, H, D, V, cap, 1e-6, norm, gate[:, 3:3 + H * V], 1e-5, sb, batch, dtype)
+        W = V + 4
+        keep = torch.zeros(H, D, W, dtype=torch.bool)
+        keep[:, :, :V + 1] = True                               # the three unused columns of a row are not compared
+        keep = torch.cat([keep.flatten(), torch.ones(H, dtype=torch.bool)])
+        assert close(ya, yb, 2e-4 if dtype == torch.float32 else 3e-2) and close(sa.cpu()[:, keep], sb[:, keep], 1e-4), (H, D, V)
+    # the selective scan
+    for I, N in ((40, 6), (24, 1), (256, 24), (11, 3), (300, 16), (64, 33)):
+        x, dt, dtb, A = rnd(T, I), f32(T, I), f32(I), -torch.rand(I, N, generator=g) * 2
+        BC, Dv, z = rnd(T, 2 * N + 5), f32(I), rnd(T, I + 3)
+        st = f32(5, I * N + 4) * 0.3
+        sa, sb = st.clone().to(dev), st.clone()
+        ya = ops.selective_scan(x.to(dev), dt.to(dev), dtb.to(dev), A.to(dev), BC.to(dev)[:, 2:2 + N], BC.to(dev)[:, 2 + N:2 + 2 * N], Dv.to(dev),
+                                z.to(dev)[:, 3:], sa, dbatch, dtype)
+        yb = ref.selective_scan(x, dt, dtb, A, BC[:, 2:2 + N], BC[:, 2 + N:2 + 2 * N], Dv, z[:, 3:], sb, batch, dtype)
+        assert close(ya, yb, 1e-4 if dtype == torch.float32 else tol) and close(sa, sb, 1e-4), (I, N)
+    # sigmoid router with rider rows; experts weighted on their input, the shared expert gated
+    for T2, hid, E, top, F, extra in ((13, 44, 6, 2, 10, 1), (70, 128, 16, 5, 64, 0), (5, 33, 7, 7, 9, 1), (40, 64, 8, 1, 64, 1), (900, 192, 8, 1, 128, 1)):
+        h, router = rnd(T2, hid), rnd(E + extra, hid) * 0.5
+        ca, wa, ea = ops.route_topk(h.to(dev), router.to(dev), None, top, None, score="sigmoid", extra_rows=extra)
+        cb, wb, eb = ref.route_topk(h, router, None, top, None, score="sigmoid", extra_rows=extra)
+        assert torch.equal(ca.cpu(), cb) and close(wa, wb, 1e-5) and (extra == 0 or close(ea, eb, 1e-4))
+        w_in, w_out, shared = rnd(E, 2 * F, hid) * 0.3, rnd(E, hid, F) * 0.3, rnd(T2, hid)
+        for sh, sg in ((None, None), (shared, None), (shared, eb)):
+            if sh is not None and sg is None and extra:
+                continue
+            for tc, tc5 in (((False, False), (True, False), (True, True)) if dtype == torch.bfloat16 else ((False, False),)):
+                keep = (ops.moe_tc, ops.moe_tcgen05)
+                ops.moe_tc, ops.moe_tcgen05 = tc and keep[0], tc5 and keep[1]
+                try:
+                    got = ops.expert_ffn(h.to(dev), ca, wa, w_in.to(dev), w_out.to(dev), 1e30, 1.0, None if sh is None else sh.to(dev), up_shift=0.0,
+                                         weight_on_input=True, shared_gate=None if sg is None else ea)
+                finally:
+                    ops.moe_tc, ops.moe_tcgen05 = keep
+                assert close(got, ref.expert_ffn(h, cb, wb, w_in, w_out, 1e30, 1.0, sh, up_shift=0.0, weight_on_input=True, shared_gate=sg)), (T2, tc, tc5)
+    ops.check_errors()
+
+
+def plain_judged(d, prompts, got):
+    """Generated tokens judged by the plain logits: each is within a rounding's reach of the largest, but for the one in six
+    that a router's near tie may send through another expert than the plain implementation's (see assert_close)."""
+    far, total = 0, 0
+    for p, out in zip(prompts, got):
+        logits = plain_logits(d, p + out)
+        for i, tok in enumerate(out):
+            row = logits[len(p) + i - 1]
+            far += int(row[tok] < row.max() - 0.12 * row.abs().max())
+            total += 1
+    assert far * 6 <= total, (far, total)
+
+
+@gpu
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_generate_through_the_entry_point_on_gpu(dirs, dtype, graphs):
+    d, cfg, page = dirs["mix"]
+    prompts = [tokens(cfg["vocab"], n, seed=40 + n) for n in (5, 13, 22, 9, 3, 30)]
+    llm = LLM(d, dtype=dtype, kv_block_size=page, kv_cache_tokens=1024, max_num_seqs=4, cuda_graphs=graphs)
+    got = llm.generate(prompts, SamplingParams(max_new_tokens=12, ignore_eos=True))
+    assert llm.cache.free_pages() == llm.cache.num_pages
+    if graphs:
+        assert llm.graphs.replays > 0
+    if dtype == "float32":
+        assert got == [plain_greedy(d, p, 12) for p in prompts]
+    else:
+        plain_judged(d, prompts, got)
+
+
+@gpu
+def test_long_decoding_on_gpu(dirs):
+    """300 tokens generated one by one after a short prompt, through the scheduler: every window slides past the prompt, pages
+    fill and new ones are taken, and the plain implementation agrees on the whole sequence at the end."""
+    d, cfg, page = dirs["pages"]
+    prompt = tokens(cfg["vocab"], 11, seed=77)
+    llm = LLM(d, dtype="float32", kv_block_size=page, kv_cache_tokens=512, max_num_seqs=2)
+    out = llm.generate([prompt], SamplingParams(max_new_tokens=300, ignore_eos=True))[0]
+    logits = plain_logits(d, prompt + out)
+    picks = logits[len(prompt) - 1:-1].argmax(-1).tolist()
+    assert sum(a == b for a, b in zip(picks, out)) >= 297          # a near tie may fall the other way; it does not derail the rest
+
+
+@gpu
+def test_trace_run_program_on_gpu(dirs, tmp_path):
+    d, cfg, page = dirs["pages"]
+    a = tokens(cfg["vocab"], 70, seed=5)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:64], "want": [0, 63]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[64:], "want": [5]}], "end": ["a"]}]
+    for dtype in ("float32", "bfloat16"):
+        out = tmp_path / dtype
+        r = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", dtype, "--out", str(out), "--max-tokens", "128"],
+                           input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        want = plain_logits(d, a)
+        g0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(2, -1))
+        g1 = torch.from_numpy(np.fromfile(out / "1.f32", dtype="<f4").reshape(1, -1))
+        assert_close(torch.cat([g0, g1]), want[[0, 63, 69]], TOL[dtype])
