@@ -277,7 +277,7 @@ def reference_arm(args):
 
 
 def design_bench(args):
-    """--design naditar | namesun: prompt and decode throughput of that design at layer sizes of real models (random weights),
+    """--design naditar | namesun | nununex: prompt and decode throughput of that design at layer sizes of real models (random weights),
     beside Qwen3 dense of the same width, depth, vocabulary and feed-forward parameters, and every new kernel beside its
     Qwen3 counterpart with its share of the bound it is up against.  One JSON line; the default workload is untouched."""
     import torch
@@ -292,7 +292,7 @@ def design_bench(args):
     for size in args.design_sizes.split(","):
         res = {}
         for name, cfg in ((args.design, design_config(size, args.design_layers, vocab)),
-                          ("qwen3", qwen3_config(size, args.design_layers, vocab))):
+                          (microbench.BESIDE.get(args.design, "qwen3"), qwen3_config(size, args.design_layers, vocab))):
             for tc in ((False, True) if name == "naditar" else (False,)):
                 llm = LLM(None, random_config=cfg, random_seed=0, dtype="bfloat16", device="cuda:0", kv_block_size=16,
                           kv_cache_tokens=64 * args.ctx + 4096, kv_watermark=0.0, max_num_seqs=64, max_model_len=args.ctx,
@@ -308,6 +308,7 @@ def design_bench(args):
                         round(d["tok_s"], 1), round(d["ms"], 4), d["launches"] // max(16, args.steps // 4)
                 llm.ops.latent_tc = False
                 res[name + ("+latent_tc" if tc else "")] = r
+                print(json.dumps({size: {name: r}}), file=sys.stderr, flush=True)
                 del llm
                 torch.cuda.empty_cache()
         out["sizes"][size] = {"layers": args.design_layers, "ctx": args.ctx, "engines": res}
@@ -320,7 +321,8 @@ def design_bench(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--design", default=None, choices=["naditar", "namesun"], help="instead of the default workload: this design beside Qwen3 at equal sizes")
+    ap.add_argument("--design", default=None, choices=["naditar", "namesun", "nununex"],
+                    help="instead of the default workload: this design beside the closest one the engine had (Qwen3; for nununex: Namesun) at equal sizes")
     ap.add_argument("--design-sizes", default="2k,4k")
     ap.add_argument("--design-layers", type=int, default=8)
     ap.add_argument("--gpus", type=int, default=1)

@@ -476,12 +476,220 @@ def bench_namesun(args, ops, peak, out=print):
     return rows
 
 
-DESIGNS = {"naditar": (naditar_config, qwen3_config_like, bench_design), "namesun": (namesun_config, qwen3_config_like_namesun, bench_namesun)}
+NUNUNEX_SIZES = {
+    # the widths, experts and attention heads of the Namesun sizes; delta-rule heads of 64 x 64, a scan of twice the width with 16
+    # states a channel, a matrix memory of 8 heads whose values are twice as wide as its keys
+    "2k": dict(width=2048, ff=8192, d_heads=32, d_dim=64, rank=64, inner=4096, state=16, dt_rank=128, conv=4, heads=16, kv_heads=8, dim=128, vdim=128,
+               window=1024, rows=32, far=4096, m_heads=8, m_dim=128, m_vdim=256, experts=32, top=4, eff=1024, shared=2048, taps=4),
+    "4k": dict(width=4096, ff=12288, d_heads=64, d_dim=64, rank=128, inner=8192, state=16, dt_rank=256, conv=4, heads=32, kv_heads=8, dim=128, vdim=128,
+               window=1024, rows=32, far=4096, m_heads=8, m_dim=256, m_vdim=512, experts=64, top=6, eff=1536, shared=3072, taps=4),
+}
+
+
+def nununex_config(size, layers, vocab=65536):
+    z = NUNUNEX_SIZES[size]
+    experts = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "expert": {"ff": z["eff"]}, "shared": {"ff": z["shared"]}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    delta = {"type": "general_delta", "mixer": {"heads": z["d_heads"], "dim": z["d_dim"], "decay_rank": z["rank"]}}
+    scan = {"type": "mamba1", "mixer": {"inner": z["inner"], "state": z["state"], "dt_rank": z["dt_rank"], "conv": z["conv"]}}
+    pair = {"type": "parallel", "mixer": {
+        "left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5, "bias_max": z["far"],
+                 "bias_rows": z["rows"], "mask": {"size": z["window"]}},
+        "right": {"heads": z["m_heads"], "dim": z["m_dim"], "vdim": z["m_vdim"], "gate_cap": 15.0}}}
+    pattern = [dict(delta, mlp=dense), dict(scan, mlp=experts), dict(delta, mlp=dense), dict(pair, mlp=experts)]
+    return {"architecture": "Nununex", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-6}, "canon": {"taps": z["taps"]}, "logit_softcap": 30.0,
+            "embedding": {"bigram": {"buckets": 1000003, "mul_prev": 1000033, "mul_cur": 7919}}, "layers": [pattern[i % 4] for i in range(layers)]}
+
+
+def namesun_config_like_nununex(size, layers, vocab=65536):
+    """Namesun (float32 stream, retention and windowed attention with a sink, routed experts) of the same width, depth, vocabulary,
+    attention heads and experts: the closest design the engine already serves."""
+    return namesun_config(size, layers, vocab)
+
+
+def bench_nununex(args, ops, peak, out=print):
+    """Each kernel of the Nununex design at the layer sizes of --design-size beside the like kernel of Namesun, with the bytes or
+    operations it cannot avoid as a share of its bound: the measured copy bandwidth, the float32 FMA rate of the CUDA cores, the
+    rate of the special-function units (one exponential per state element of the selective scan), or the measured bf16 peak."""
+    import numpy as np
+    from ..parts.base import GatedDelta
+    z = NUNUNEX_SIZES[args.design_size]
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    bf16_peak = 1590.0
+    if os.path.isfile(os.path.join(here, "MEASURED_PEAKS.json")):
+        with open(os.path.join(here, "MEASURED_PEAKS.json")) as f:
+            bf16_peak = json.load(f)["bf16_tflops"]
+    props = torch.cuda.get_device_properties(0)
+    fma_peak = props.multi_processor_count * 128 * 2 * 1.965e9 / 1e12
+    sfu_peak = props.multi_processor_count * 16 * 1.965e9 / 1e12
+    rows = []
+
+    def line(kernel, shape, us, amount, bound):
+        got, top, unit = {"hbm": (amount / us / 1e3, peak, "GB/s"), "bf16": (amount / us / 1e6, bf16_peak, "TFLOP/s"),
+                          "fma": (amount / us / 1e6, fma_peak, "TFLOP/s (fp32 FMA)"), "sfu": (amount / us / 1e6, sfu_peak, "Texp/s (SFU)")}[bound]
+        rows.append({"kernel": kernel, "shape": shape, "us": round(us, 2), "achieved": round(got, 2), "unit": unit, "frac": round(got / top, 3)})
+        out(f"{kernel:44s} {shape:46s} {us:9.2f} us {got:9.2f} {unit:20s} {100 * got / top:5.1f} % of bound", flush=True)
+
+    t = lambda a: torch.tensor(np.asarray(a, dtype=np.int32), device="cuda")       # noqa: E731
+    bf = torch.bfloat16
+    W, T, it = z["width"], args.tokens, args.iters
+    rb = lambda *s: torch.randn(*s, device="cuda", dtype=bf)                       # noqa: E731
+    rf = lambda *s: torch.randn(*s, device="cuda")                                 # noqa: E731
+
+    def entries(B, n, pos0=0):
+        return types.SimpleNamespace(seg_q_start=t(np.arange(B + 1) * n), seg_slot=t(np.arange(B) + 1), num_segs=B,
+                                     token_seg=t(np.repeat(np.arange(B), n)), positions=t(np.tile(np.arange(n), B) + pos0))
+
+    # ---- stream kernels
+    x, y, lg = rf(4, T, W), rb(4, T, W), rb(4, T, W)
+    wn, gb = torch.ones(W, device="cuda"), torch.zeros(W, device="cuda")
+    us = timed(lambda i: ops.stream_rmsnorm(x[i % 4], GatedDelta(y[i % 4], lg[i % 4], gb), wn, 1e-6, None, bf), it)
+    line("gated addition + norm (f32 stream)", f"T={T} width={W}", us, T * W * 14.0, "hbm")
+    us = timed(lambda i: ops.out_rmsnorm_add(x[i % 4], y[i % 4], wn, wn, 0.3, 1e-6, bf), it)
+    line("  Namesun: output norm + add (f32 stream)", f"T={T} width={W}", us, T * W * 12.0, "hbm")
+    us = timed(lambda i: ops.dual_rmsnorm_mix(y[i % 4], wn, 0.5, lg[i % 4], wn, 0.5, 1e-6), it)
+    line("norm and mix of two mixers' outputs", f"T={T} width={W}", us, T * W * 6.0, "hbm")
+    ids = torch.randint(0, 65536, (T,), device="cuda", dtype=torch.int32)
+    table, pairs, prev = rb(65536, W), rb(1000004, W), torch.zeros(2, 1, dtype=torch.int32, device="cuda")
+    e1 = entries(1, T)
+    us = timed(lambda i: ops.embed_bigram_stream(ids, table, pairs, 1000003, 1000033, 7919, prev, e1), it)
+    line("embedding + hashed pair row", f"T={T} width={W}", us, T * W * 8.0, "hbm")
+    us = timed(lambda i: ops.embed_stream(ids, table, bf), it)
+    line("  Namesun: embedding", f"T={T} width={W}", us, T * W * 8.0, "hbm")
+    del table, pairs
+    cw = rf(W, z["taps"])
+    for B, n in ((1, T), (64, 1)):
+        st = torch.zeros(B + 1, (z["taps"] - 1) * W, device="cuda")
+        hh, e = rb(4, B * n, W), entries(B, n)
+        us = timed(lambda i: ops.short_conv(hh[i % 4], cw, None, z["taps"], st, 0, e, residual=True), it)
+        line("input filter (causal convolution + input)", f"B={B} T={n} width={W} taps={z['taps']}", us,
+             B * n * W * 4.0 + (B * (z["taps"] - 1) * W * 8.0 if n == 1 else 0), "hbm")
+    F = z["ff"]
+    zz, fb = rb(4, T, F), torch.zeros(F, device="cuda")
+    us = timed(lambda i: ops.bias_act(zz[i % 4], fb, "relu2"), it)
+    line("bias + squared relu", f"T={T} ff={F}", us, T * F * 4.0, "hbm")
+    gu = rb(4, T, 2 * z["shared"])
+    us = timed(lambda i: ops.clamped_glu(gu[i % 4], 7.0, 1.702), it)
+    line("  Namesun: clamped gated activation", f"T={T} inter={z['shared']}", us, T * z["shared"] * 6.0, "hbm")
+    del zz, gu
+    # ---- the three recurrences beside Namesun's retention: one prompt of T tokens; decode steps of B requests
+    H, D, R = z["d_heads"], z["d_dim"], z["rank"]
+    w2, w0, ab = rb(H * D, R) * 0.1, torch.zeros(H * D, device="cuda"), torch.zeros(H * D, device="cuda")
+    for B, n in ((1, T), (8, 1), (64, 1)):
+        rows_n, e = B * n, entries(B, n, 0 if n > 1 else 4095)
+        kind = "prompt" if n > 1 else "decode"
+        reps = 4 if n > 1 else max(2, (256 << 20) // (B * H * D * D * 4) + 1)
+        p = rb(rows_n, 5 * H * D + R)
+        st = torch.zeros(reps, B + 1, H * D * D, device="cuda")
+        us = timed(lambda i: ops.general_delta_prepare(p, w2, w0, ab, H, D, D, R, 0.6, 1e-6), it)
+        line("delta rule: unit key, decay, removal", f"{kind} B={B} T={n} heads={H} {D}x{D}", us, rows_n * ((5 * H * D + R) * 2.0 + 6 * H * D * 4.0), "hbm")
+        prep = ops.general_delta_prepare(p, w2, w0, ab, H, D, D, R, 0.6, 1e-6)
+        us = timed(lambda i: ops.general_delta_scan(prep, H, D, D, st[i % reps], e), it)
+        line("delta rule: scan", f"{kind} B={B} T={n} heads={H} {D}x{D}", us, 10.0 * H * D * D * rows_n if n > 1 else 8.0 * B * H * D * D, "fma" if n > 1 else "hbm")
+        del st
+        H2, D2, V2 = z["heads"], z["dim"], z["vdim"]
+        reps = 4 if n > 1 else max(2, (256 << 20) // (B * H2 * D2 * V2 * 4) + 1)
+        p2, decay = rb(rows_n, 2 * H2 * D2 + 2 * H2 * V2), torch.full((H2,), 0.99, device="cuda")
+        inv = (1e6 ** (-torch.arange(0, D2, 2, dtype=torch.float64) / D2)).float().cuda()
+        st = torch.zeros(reps, B + 1, H2 * D2 * V2, device="cuda")
+        us = timed(lambda i: ops.retention_scan(p2, H2, D2, V2, inv, D2 ** -0.5, decay, st[i % reps], e), it)
+        line("  Namesun: retention (rotation + scan)", f"{kind} B={B} T={n} heads={H2} {D2}x{V2}", us,
+             4.0 * H2 * D2 * V2 * rows_n if n > 1 else 8.0 * B * H2 * D2 * V2, "fma" if n > 1 else "hbm")
+        del st
+        H3, D3, V3 = z["m_heads"], z["m_dim"], z["m_vdim"]
+        Wd = V3 + 4
+        reps = 4 if n > 1 else max(2, (256 << 20) // (B * H3 * D3 * Wd * 4) + 1)
+        p3, gl, gbias = rb(rows_n, 2 * H3 * D3 + 2 * H3 * V3), rf(rows_n, 2 * H3), torch.zeros(2 * H3, device="cuda")
+        norm3 = torch.ones(H3 * V3, device="cuda")
+        st = torch.zeros(reps, B + 1, H3 * D3 * Wd + H3, device="cuda")
+        us = timed(lambda i: ops.matrix_memory(p3, gl, gbias, H3, D3, V3, 15.0, 1e-6, norm3, p3[:, 2 * H3 * D3 + H3 * V3:], 1e-6, st[i % reps], e, bf), it)
+        line("matrix memory: gates, scan, norm, gate", f"{kind} B={B} T={n} heads={H3} {D3}x{V3}", us,
+             4.0 * H3 * D3 * Wd * rows_n if n > 1 else 8.0 * B * H3 * D3 * Wd, "fma" if n > 1 else "hbm")
+        del st
+        I, N = z["inner"], z["state"]
+        reps = 4 if n > 1 else max(2, (256 << 20) // (B * I * N * 4) + 1)
+        xs, dt, bc, zs = rb(rows_n, I), rf(rows_n, I), rb(rows_n, 2 * N), rb(rows_n, I)
+        A, dtb, Dv = -torch.rand(I, N, device="cuda"), torch.zeros(I, device="cuda"), torch.ones(I, device="cuda")
+        st = torch.zeros(reps, B + 1, I * N, device="cuda")
+        us = timed(lambda i: ops.selective_scan(xs, dt, dtb, A, bc[:, :N], bc[:, N:], Dv, zs, st[i % reps], e, bf), it)
+        line("selective scan", f"{kind} B={B} T={n} inner={I} state={N}", us, 1.0 * I * N * rows_n if n > 1 else 8.0 * B * I * N, "sfu" if n > 1 else "hbm")
+        del st
+    # ---- windowed attention with distance rows and a learned sink beside Namesun's attention in blocks
+    H, KV, D, V = z["heads"], z["kv_heads"], z["dim"], z["vdim"]
+    ps, win = 16, z["window"]
+    pages = -(-T // ps)
+    table = (torch.randperm(pages, device="cuda").to(torch.int32) + 1).view(1, pages).contiguous()
+    meta = types.SimpleNamespace(page_size=ps, tile=64, block_table=table, table_rows=t([0]), max_pages=pages, seg_q_start=t([0, T]), seg_pos0=t([0]),
+                                 seg_kv_len=t([T]), decode_segs=t([]), max_kv_len=T, num_tokens=T, positions=t(np.arange(T)), slots=t(np.arange(T) + ps),
+                                 prefill_tiles=t([(0, r) for r in range(0, T, 64)]).view(-1, 2), prefill_tiles2=t([(0, r) for r in range(0, T, 128)]).view(-1, 2))
+    kv = rb(4, 2, pages + 1, KV, ps, D)
+    qq = rb(T, H * D)
+    sinks, bias = rf(H), rf(z["far"] + 1, H) * 0.1
+    bias_h = bias.t().contiguous()
+    pairs_win = sum(min(p + 1, win) for p in range(T))
+    us = timed(lambda i: ops.masked_attention(qq, kv[i % 4, 0], kv[i % 4, 1], meta, H, KV, D, V, D ** -0.5, None, win, True, sink_values=sinks, distance_bias=bias,
+                                              distance_bias_by_head=bias_h), it)
+    bound = "bf16" if getattr(ops, "biased_attention_tc", False) else "fma"
+    line("attention: window, distance rows, learned sink", f"prompt T={T} heads={H}/{KV} D={D} window={win}", us, 2.0 * H * (D + V) * pairs_win, bound)
+    us = timed(lambda i: ops.masked_attention(qq, kv[i % 4, 0], kv[i % 4, 1], meta, H, KV, D, V, 0.7, win, None, True), it)
+    line("  Namesun: attention in blocks, sink (split weights)", f"prompt T={T} heads={H}/{KV} D={D} block={win}", us,
+         2.0 * H * (D + V) * sum((p % win) + 1 for p in range(T)), "bf16")
+    ctx = args.ctx
+    pages = -(-ctx // ps)
+    for B in (8, 64):
+        layers = max(2, (512 << 20) // (B * pages * ps * KV * D * 4) + 1)
+        table = (torch.stack([torch.randperm(pages, device="cuda") for _ in range(B)]) + 1 + (torch.arange(B, device="cuda") * pages)[:, None]).to(torch.int32)
+        ar = torch.arange(B + 1, dtype=torch.int32, device="cuda")
+        meta = types.SimpleNamespace(page_size=ps, tile=64, block_table=table.contiguous(), table_rows=ar[:B].contiguous(), max_pages=pages, seg_q_start=ar,
+                                     seg_pos0=torch.full((B,), ctx - 1, dtype=torch.int32, device="cuda"),
+                                     seg_kv_len=torch.full((B,), ctx, dtype=torch.int32, device="cuda"), decode_segs=ar[:B].contiguous(),
+                                     prefill_tiles=torch.zeros((0, 2), dtype=torch.int32, device="cuda"), prefill_tiles2=None, max_kv_len=ctx, num_tokens=B)
+        kv = rb(layers, 2, B * pages + 1, KV, ps, D)
+        qq = rb(B, H * D)
+        seen = min(ctx, win)
+        us = timed(lambda i: ops.masked_attention(qq, kv[i % layers, 0], kv[i % layers, 1], meta, H, KV, D, V, D ** -0.5, None, win, True, sink_values=sinks,
+                                                  distance_bias=bias, distance_bias_by_head=bias_h), it)
+        line("attention: window, distance rows, learned sink", f"decode B={B} ctx={ctx} sees {seen} heads={H}/{KV}", us, B * seen * KV * (D + V) * 2.0, "hbm")
+        us = timed(lambda i: ops.masked_attention(qq, kv[i % layers, 0], kv[i % layers, 1], meta, H, KV, D, V, 0.7, win, None, True), it)
+        line("  Namesun: attention in blocks, sink", f"decode B={B} ctx={ctx} sees {(ctx - 1) % win + 1} heads={H}/{KV}", us,
+             B * ((ctx - 1) % win + 1) * KV * (D + V) * 2.0, "hbm")
+        del kv
+    # ---- sigmoid router with the shared gate's row; experts weighted on their input beside experts weighted on their output
+    E, top, F = z["experts"], z["top"], z["eff"]
+    for rows_n in (T, 64, 8):
+        h = rb(rows_n, W)
+        router, corr = rb(E + 1, W) * 0.05, torch.zeros(E, device="cuda")
+        reps = 4 if rows_n > 64 else max(2, (300 << 20) // (E * 3 * F * W * 2) + 1)
+        w_in, w_out = rb(reps, E, 2 * F, W) * 0.02, rb(reps, E, W, F) * 0.02
+        us = timed(lambda i: ops.route_topk(h, router, None, top, None, score="sigmoid", extra_rows=1), it)
+        line("router: logits, sigmoid, top-k, gate row", f"rows={rows_n} experts={E} top={top}", us, rows_n * W * 2.0 + (E + 1) * W * 2.0, "hbm")
+        us = timed(lambda i: ops.route_topk(h, router[:E].contiguous(), corr, top, None), it)
+        line("  Namesun: router (softmax, top-k)", f"rows={rows_n} experts={E} top={top}", us, rows_n * W * 2.0 + E * W * 2.0, "hbm")
+        chosen, wts, gate_row = ops.route_topk(h, router, None, top, None, score="sigmoid", extra_rows=1)
+        shared = rb(rows_n, W)
+        flops, hit = 2.0 * rows_n * top * 3 * F * W, min(E, rows_n * top)
+        amount, bound = (flops, "bf16") if rows_n > 64 else (hit * 3.0 * F * W * 2, "hbm")
+        us = timed(lambda i: ops.expert_ffn(h, chosen, wts, w_in[i % reps], w_out[i % reps], float("inf"), 1.0, shared, up_shift=0.0, weight_on_input=True,
+                                            shared_gate=gate_row), it)
+        line("experts weighted on their input, gated shared", f"rows={rows_n} experts={E} top={top} ff={F}", us, amount, bound)
+        us = timed(lambda i: ops.expert_ffn(h, chosen, wts, w_in[i % reps], w_out[i % reps], 7.0, 1.702, shared), it)
+        line("  Namesun: experts weighted on their output", f"rows={rows_n} experts={E} top={top} ff={F}", us, amount, bound)
+        del w_in, w_out
+    lo = rf(64, 65536)
+    us = timed(lambda i: ops.softcap(lo, 30.0), it)
+    line("soft cap of the logits", "rows=64 vocab=65536", us, 64 * 65536 * 8.0, "hbm")
+    ops.check_errors()
+    return rows
+
+
+DESIGNS = {"naditar": (naditar_config, qwen3_config_like, bench_design), "namesun": (namesun_config, qwen3_config_like_namesun, bench_namesun),
+           "nununex": (nununex_config, namesun_config_like_nununex, bench_nununex)}
+BESIDE = {"nununex": "namesun"}            # the design an entry of DESIGNS is set beside (default: qwen3)
 
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("what", choices=["gemm", "attention", "prefill", "design", "namesun"])
+    ap.add_argument("what", choices=["gemm", "attention", "prefill", "design", "namesun", "nununex"])
     ap.add_argument("--design-size", default="2k", choices=sorted(NADITAR_SIZES), help="design: layer sizes of the Naditar kernels")
     ap.add_argument("--size", default="4b", choices=sorted(SIZES))
     ap.add_argument("--rows", default="1,8,64", type=lambda s: [int(v) for v in s.split(",")])
@@ -500,7 +708,7 @@ def main(argv=None):
     ops = get_ops("cuda:0")
     peak, src = peak_gbs()
     print(f"# peak {peak} GB/s ({src})")
-    {"gemm": bench_gemm, "attention": bench_attention, "prefill": bench_prefill_attention, "design": bench_design, "namesun": bench_namesun}[args.what](args, ops, peak)
+    {"gemm": bench_gemm, "attention": bench_attention, "prefill": bench_prefill_attention, "design": bench_design, "namesun": bench_namesun, "nununex": bench_nununex}[args.what](args, ops, peak)
     return 0
 
 

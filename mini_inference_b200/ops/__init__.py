@@ -127,6 +127,8 @@ class CudaOps:
         self.skinny_gemm = True              # few-row products on this package's weight-streaming kernel ...
         self.skinny_max_rows, self.skinny_max_cols = 16, 4096    # ... where it is at least as fast as the library's
         self.fast_attention = True           # tests clear this to run the generic attention kernels in bfloat16
+        self.biased_attention_tc = True      # prompts of attention with a distance table or a learned sink on the tensor cores (bfloat16)
+        self._zero_bias = {}
         # Latent attention whose cached rows have 64 or 128 entries can run on the tensor-core paged attention kernels.  Those
         # round the softmax weights to bfloat16 before the weighted sum; a design that asks for float32 weights gets the
         # float32 kernels of csrc/attention_latent.cu unless MI_LATENT_TC=1 (or this flag) says otherwise.
@@ -835,11 +837,13 @@ class CudaOps:
         self.launches += 1
         return p[:, :H * D]
 
-    def masked_attention(self, q, k_cache, v_cache, meta, H, KV, D, V, scale, block_size, window, sink, sink_values=None, distance_bias=None):
+    def masked_attention(self, q, k_cache, v_cache, meta, H, KV, D, V, scale, block_size, window, sink, sink_values=None, distance_bias=None,
+                         distance_bias_by_head=None):
         """q [T, H D] (a strided view is allowed) over the pages; keys of D and values of V entries; block_size / window / sink as
         csrc/attention_masked.cu states them.  sink_values float32 [H]: the sink's score per head (None: 0); distance_bias float32
-        [far + 1, H]: added to the scaled score by the distance i - j (beyond far: the last row).  Scores, weights and sums are
-        float32.  Returns [T, H V]."""
+        [far + 1, H]: added to the scaled score by the distance i - j (beyond far: the last row); distance_bias_by_head: the same
+        table as float32 [H, far + 1], for the kernels that read it along the distance.  Scores, weights and sums are float32.
+        Returns [T, H V]."""
         T = q.shape[0]
         assert q.stride(1) == 1
         out = torch.empty((T, H * V), dtype=q.dtype, device=q.device)
@@ -859,6 +863,15 @@ class CudaOps:
                 _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(meta.prefill_tiles), num_tiles, _p(meta.seg_q_start),
                 _p(meta.seg_pos0), _p(meta.block_table), _p(rows), meta.max_pages, H, KV, D, meta.page_size, meta.tile,
                 _c.c_float(scale), win, blk, int(bool(sink)), self._stream()), "attn_prefill_mma_masked")
+            self.launches += 1
+        elif (num_tiles and self.fast_attention and self.biased_attention_tc and q.dtype == torch.bfloat16 and D == V and D in (64, 128)
+                and meta.tile == 64 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
+            # the same kernel with the learned sink's score and the distance table (one row per head) in its softmax
+            bias_t = self._bias_rows_by_head(distance_bias, distance_bias_by_head, H, q.device)
+            _check(self.lib.mi_attn_prefill_mma_biased(
+                _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(meta.prefill_tiles), num_tiles, _p(meta.seg_q_start),
+                _p(meta.seg_pos0), _p(meta.block_table), _p(rows), meta.max_pages, H, KV, D, meta.page_size, meta.tile,
+                _c.c_float(scale), win, blk, int(bool(sink)), _p(sink_values), _p(bias_t), bias_t.shape[1] - 1, self._stream()), "attn_prefill_mma_biased")
             self.launches += 1
         elif num_tiles:
             _check(self.lib.mi_masked_prefill(
@@ -907,6 +920,19 @@ class CudaOps:
                 self._stream()), "masked_decode")
             self.launches += 2 if S > 1 else 1
         return out
+
+    def _bias_rows_by_head(self, distance_bias, by_head, H, device):
+        """The distance table [far + 1, H] one row per head, [H, far + 1]: the caller's own copy if it keeps one, else made here;
+        no table at all (a learned sink alone): one zero a head."""
+        if by_head is not None:
+            assert by_head.dtype == torch.float32 and by_head.is_contiguous() and by_head.shape[0] == H
+            return by_head
+        if distance_bias is not None:
+            return distance_bias.t().contiguous()
+        zero = self._zero_bias.get(H)
+        if zero is None:
+            zero = self._zero_bias[H] = torch.zeros((H, 1), dtype=torch.float32, device=device)
+        return zero
 
     # ---------------------------------------------------------------- retention
     def retention_scan(self, p, H, D, V, inv_freq, k_scale, decay, state, batch):

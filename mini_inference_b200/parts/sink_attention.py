@@ -51,7 +51,7 @@ class SinkAttention(Part):
             raise ValueError(f"{self.H} query heads are not a multiple of {self.KV} kv heads")
         if self.value_mix not in (None, "source", "blend"):
             raise ValueError(f"value_mix '{self.value_mix}' is not one of source, blend")
-        self.qkv = self.o = self.lam = self.sink_values = self.bias_by_distance = None
+        self.qkv = self.o = self.lam = self.sink_values = self.bias_by_distance = self.bias_by_head = None
 
     def weight_specs(self):
         H, KV, D, V, hid = self.H, self.KV, self.D, self.V, self.hidden
@@ -88,6 +88,7 @@ class SinkAttention(Part):
                 raise ValueError("distance_bias needs at least two rows and a far distance beyond half of them")
             index = torch.tensor([self.distance_row(n, rows, far) for n in range(far + 1)], dtype=torch.long, device=device)
             self.bias_by_distance = tensors["rel"].float()[index].contiguous()          # [far + 1, H]; distances beyond far read the last row
+            self.bias_by_head = self.bias_by_distance.t().contiguous()                  # [H, far + 1]: the same, read along the distance
 
     step_arrays = staticmethod(paged_attention_step_arrays)
 
@@ -113,7 +114,8 @@ class SinkAttention(Part):
                               cache.k if owns_cache else None, cache.v if owns_cache else None)
         if self.learned_sink or self.distance_bias:
             o = ops.masked_attention(q, cache.k, cache.v, meta, H, KV, D, V, self.scale, self.block_size, self.window, self.sink,
-                                     sink_values=self.sink_values, distance_bias=self.bias_by_distance)
+                                     sink_values=self.sink_values, distance_bias=self.bias_by_distance,
+                                     distance_bias_by_head=self.bias_by_head)
         else:
             o = ops.masked_attention(q, cache.k, cache.v, meta, H, KV, D, V, self.scale, self.block_size, self.window, self.sink)
         return ops.linear(o, self.o)

@@ -524,7 +524,7 @@ _plain_masked_attention = _masked_attention
 
 
 def _masked_attention_biased(self, q, k_cache, v_cache, meta, H, KV, D, V, scale, block_size, window, sink, sink_values=None,
-                             distance_bias=None):
+                             distance_bias=None, distance_bias_by_head=None):
     if sink_values is None and distance_bias is None:
         return _plain_masked_attention(self, q, k_cache, v_cache, meta, H, KV, D, V, scale, block_size, window, sink)
     T = q.shape[0]

@@ -729,8 +729,9 @@ def test_recurrences_remember_a_far_token_on_gpu():
 
 
 @gpu
+@pytest.mark.parametrize("lens,slots,starts", [([1, 23, 6, 2], [3, 1, 4, 2], [40, 0, 100, 0]), ([600, 1, 59], [2, 4, 1], [0, 7, 300])])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_kernels_against_the_stand_ins(dtype):
+def test_kernels_against_the_stand_ins(dtype, lens, slots, starts):
     """Every kernel of the design alone, at sizes no model above has (odd ones too), several entries of unequal length in one
     launch, states that start non-zero and slots out of order, against the plain PyTorch statement of the same op."""
     from mini_inference_b200.parts.base import GatedDelta
@@ -740,12 +741,13 @@ def test_kernels_against_the_stand_ins(dtype):
     rnd = lambda *s: torch.randn(*s, generator=g).to(dtype)      # noqa: E731
     f32 = lambda *s: torch.randn(*s, generator=g)                # noqa: E731
     close = lambda a, b, t=tol: (a.float().cpu() - b.float().cpu()).abs().max() <= t * max(1.0, b.float().abs().max().item())  # noqa: E731
-    lens, slots, qs, T = [1, 23, 6, 2], [3, 1, 4, 2], [0, 1, 24, 30, 32], 32
-    pos = [40] + list(range(0, 23)) + list(range(100, 106)) + [0, 1]
-    seg = [0] + [1] * 23 + [2] * 6 + [3] * 2
-    batch = SimpleNamespace(host={"seg_q_start": qs, "seg_slot": slots}, num_segs=4, positions=_i32(pos, "cpu"), token_seg=_i32(seg, "cpu"),
+    qs, T, n = [0] + list(np.cumsum(lens)), sum(lens), len(lens)
+    qs = [int(v) for v in qs]
+    pos = [p0 + i for p0, ln in zip(starts, lens) for i in range(ln)]
+    seg = [i for i, ln in enumerate(lens) for _ in range(ln)]
+    batch = SimpleNamespace(host={"seg_q_start": qs, "seg_slot": slots}, num_segs=n, positions=_i32(pos, "cpu"), token_seg=_i32(seg, "cpu"),
                             seg_q_start=_i32(qs, "cpu"), seg_slot=_i32(slots, "cpu"))
-    dbatch = SimpleNamespace(num_segs=4, positions=_i32(pos, dev), token_seg=_i32(seg, dev), seg_q_start=_i32(qs, dev), seg_slot=_i32(slots, dev))
+    dbatch = SimpleNamespace(num_segs=n, positions=_i32(pos, dev), token_seg=_i32(seg, dev), seg_q_start=_i32(qs, dev), seg_slot=_i32(slots, dev))
     # pair embedding: the previous token of an entry comes from its slot; position 0 takes the last row
     for hid, buckets, mp, mc in ((77, 13, 5, 3), (192, 1, 7, 2), (40, 509, 2 ** 31 - 1, 2 ** 29 + 3)):
         ids, table, pairs = torch.randint(0, 50, (T,), generator=g, dtype=torch.int32), rnd(50, hid), rnd(buckets + 1, hid)
