@@ -78,7 +78,7 @@ constexpr int DEC_WARPS_ALONE = 8; // warps of a block that has its SM to itself
 //               in flight per SM at no register cost.
 // SPLIT: every softmax weight enters the P V product as two bfloat16 numbers, its rounding and what the rounding left behind
 // (16 mantissa bits in all, summed in float32), for designs that want their attention weights in more than 16-bit precision.
-template <int D, bool BULK, int WARPS, bool SPLIT = false>
+template <int D, bool BULK, int WARPS, bool SPLIT = false, bool BIAS = false>
 __global__ void __launch_bounds__(WARPS * 32, WARPS > DEC_WARPS ? 1 : BULK ? 2 : 3)
 attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                        const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_cache,
@@ -87,7 +87,10 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
                        const int* __restrict__ seg_q_start, const int* __restrict__ seg_kv_len,
                        const int* __restrict__ block_table, const int* __restrict__ table_rows, int table_stride,
                        int H, int KV, int ps, float scale_log2, int window, int* __restrict__ merge_counters,
-                       int* __restrict__ error_word, int cluster_merge, int block, int sink) {
+                       int* __restrict__ error_word, int cluster_merge, int block, int sink,
+                       const float* __restrict__ sink_values, const float* __restrict__ bias_t, int bias_last) {
+    // BIAS: bias_t float32 [H, bias_last + 1] is added to the scaled score by the distance len - 1 - key (beyond bias_last: the last
+    // entry), one row per head; sink_values float32 [H] (or null: 0) is the score of the sink.
     // block > 0: the query (position len - 1) sees only the keys of its own block of positions, from floor((len - 1) / block) * block on.
     // sink != 0: the softmax has one more term of score 0 that carries no value; ONE warp of ONE split starts its running maximum
     // at 0 and its running sum at 1, and the merges of warps and of splits carry the term along like any other.
@@ -176,7 +179,13 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
 #pragma unroll
     for (int t = 0; t < NT; ++t) { o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f; }
     const bool has_sink = sink && s == 0 && warp == 0;
-    float m0 = has_sink ? 0.f : -INFINITY, m1 = m0, l0 = has_sink && c == 0 ? 1.f : 0.f, l1 = l0;      // rows g and g + 8; sums are per thread
+    constexpr float LOG2E = 1.4426950408889634f;
+    const int head0 = kvh * G + min(g, G - 1), head1 = kvh * G + min(g + 8, G - 1);        // rows beyond G are padding
+    const float* __restrict__ bias_row0 = BIAS ? bias_t + (size_t)head0 * (bias_last + 1) : nullptr;
+    const float* __restrict__ bias_row1 = BIAS ? bias_t + (size_t)head1 * (bias_last + 1) : nullptr;
+    float m0 = has_sink ? (BIAS && sink_values ? sink_values[head0] * LOG2E : 0.f) : -INFINITY;
+    float m1 = has_sink ? (BIAS && sink_values ? sink_values[head1] * LOG2E : 0.f) : -INFINITY;
+    float l0 = has_sink && c == 0 ? 1.f : 0.f, l1 = l0;                                    // rows g and g + 8; sums are per thread
 
     uint4 kreg[2][KS / 2];
     uint4 vreg[4][HALVES];
@@ -261,8 +270,14 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
             for (int e = 0; e < 2; ++e) {
                 const int key = blk * 16 + nt * 8 + 2 * c + e;
                 const bool ok = key >= lo && key < len;
-                sc[nt][e] = ok ? sc[nt][e] * scale_log2 : -INFINITY;
-                sc[nt][2 + e] = ok ? sc[nt][2 + e] * scale_log2 : -INFINITY;
+                if (BIAS) {
+                    const int dist = min(max(len - 1 - key, 0), bias_last);
+                    sc[nt][e] = ok ? fmaf(sc[nt][e], scale_log2, bias_row0[dist] * LOG2E) : -INFINITY;
+                    sc[nt][2 + e] = ok ? fmaf(sc[nt][2 + e], scale_log2, bias_row1[dist] * LOG2E) : -INFINITY;
+                } else {
+                    sc[nt][e] = ok ? sc[nt][e] * scale_log2 : -INFINITY;
+                    sc[nt][2 + e] = ok ? sc[nt][2 + e] * scale_log2 : -INFINITY;
+                }
                 mx0 = fmaxf(mx0, sc[nt][e]);
                 mx1 = fmaxf(mx1, sc[nt][2 + e]);
             }
@@ -527,13 +542,14 @@ MI_EXPORT int mi_attn_decode_cluster_fit(int D, int splits) {
 // the device) and entry i reads row table_rows[i]; null: entry i reads row i.  cluster_merge != 0: with 2..8 splits the
 // splits of a (request, kv head) are launched as one thread-block cluster and merged through distributed shared memory
 // (o_part, lse_part, merge_counters unused).
-template <bool SPLIT>
+template <bool SPLIT, bool BIAS = false>
 static int decode_mma_rows_launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
                                   float* o_part, float* lse_part, const int* decode_segs, int num_decode,
                                   const int* seg_q_start, const int* seg_kv_len, const int* block_table,
                                   const int* table_rows, int table_stride, int H, int KV, int D, int ps, int splits,
                                   float scale, int window, int* merge_counters, int* error_word, int cache_pages,
-                                  int cluster_merge, cudaStream_t stream, int block = 0, int sink = 0) {
+                                  int cluster_merge, cudaStream_t stream, int block = 0, int sink = 0,
+                                  const float* sink_values = nullptr, const float* bias_t = nullptr, int bias_last = 0) {
     if (num_decode == 0) return 0;
     if ((D != 64 && D != 128) || H % KV || H / KV > 16 || ps % 16 || q_stride % 8) return -2;
     dim3 grid(num_decode, KV, splits);
@@ -562,7 +578,7 @@ static int decode_mma_rows_launch(const void* q, int q_stride, const void* k_cac
 #define LAUNCH(DD, BB, WW) do { \
         static bool configured = false; \
         if (!configured && smem > 48 * 1024) { \
-            cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<DD, BB, WW, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<DD, BB, WW, SPLIT, BIAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) return (int)e; \
             configured = true; \
         } \
@@ -580,17 +596,17 @@ static int decode_mma_rows_launch(const void* q, int q_stride, const void* k_cac
             if (fit[splits] == 0) { \
                 cfg.attrs = attr; cfg.numAttrs = 1; \
                 int n = 0; \
-                if (cudaOccupancyMaxActiveClusters(&n, attn_decode_mma_kernel<DD, BB, WW, SPLIT>, &cfg) != cudaSuccess || n < 1) n = -1; \
+                if (cudaOccupancyMaxActiveClusters(&n, attn_decode_mma_kernel<DD, BB, WW, SPLIT, BIAS>, &cfg) != cudaSuccess || n < 1) n = -1; \
                 fit[splits] = n; \
             } \
             /* (with a margin: blocks of the kernels before and after share the SMs for a moment) */ \
             if (fit[splits] < 0 || (long long)num_decode * KV * 100 > (long long)fit[splits] * 92) use_cluster = 0; \
         } \
         cfg.attrs = use_cluster ? attr : attr + 1; cfg.numAttrs = use_cluster ? 2 : 1; \
-        return (int)cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<DD, BB, WW, SPLIT>, kmap, vmap, \
+        return (int)cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<DD, BB, WW, SPLIT, BIAS>, kmap, vmap, \
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
             (__nv_bfloat16*)out, o_part, lse_part, decode_segs, seg_q_start, seg_kv_len, block_table, table_rows, \
-            table_stride, H, KV, ps, scale_log2, window, merge_counters, error_word, use_cluster, block, sink); } while (0)
+            table_stride, H, KV, ps, scale_log2, window, merge_counters, error_word, use_cluster, block, sink, sink_values, bias_t, bias_last); } while (0)
     if (D == 128) { if (alone) LAUNCH(128, true, DEC_WARPS_ALONE); else if (bulk) LAUNCH(128, true, DEC_WARPS); else LAUNCH(128, false, DEC_WARPS); }
     else { if (alone) LAUNCH(64, true, DEC_WARPS_ALONE); else if (bulk) LAUNCH(64, true, DEC_WARPS); else LAUNCH(64, false, DEC_WARPS); }
 #undef LAUNCH
@@ -626,5 +642,18 @@ MI_EXPORT int mi_attn_decode_mma_rows_masked(const void* q, int q_stride, const 
                                              float scale, int window, int* merge_counters, int* error_word, int cache_pages,
                                              int cluster_merge, int block, int sink, cudaStream_t stream) {
     return decode_mma_rows_launch<true>(DECODE_ROWS_ARGS, block, sink);
+}
+
+// The masked form with a learned score of the sink per head (sink_values float32 [H], or null: 0) and a learned addition to the
+// scaled score by distance (bias_t float32 [H, bias_last + 1]; distances beyond bias_last read the last entry).
+MI_EXPORT int mi_attn_decode_mma_rows_biased(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                             float* o_part, float* lse_part, const int* decode_segs, int num_decode,
+                                             const int* seg_q_start, const int* seg_kv_len, const int* block_table,
+                                             const int* table_rows, int table_stride, int H, int KV, int D, int ps, int splits,
+                                             float scale, int window, int* merge_counters, int* error_word, int cache_pages,
+                                             int cluster_merge, int block, int sink, const float* sink_values, const float* bias_t,
+                                             int bias_last, cudaStream_t stream) {
+    if (!bias_t) return -2;
+    return decode_mma_rows_launch<true, true>(DECODE_ROWS_ARGS, block, sink, sink_values, bias_t, bias_last);
 }
 #undef DECODE_ROWS_ARGS

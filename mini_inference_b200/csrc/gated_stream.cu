@@ -99,6 +99,29 @@ __global__ void bias_act_kernel(const T* __restrict__ z, const float* __restrict
     }
 }
 
+// the same, eight bfloat16 numbers (16 bytes) a thread; cols is a multiple of 8, so the eight share a row
+__global__ void bias_act_vec_kernel(const uint4* __restrict__ z, const float* __restrict__ bias, uint4* __restrict__ out, size_t n8, int cols, int act) {
+    for (size_t i = (size_t)blockIdx.x * NT + threadIdx.x; i < n8; i += (size_t)gridDim.x * NT) {
+        const uint4 v = z[i];
+        const int c = (int)((i * 8) % (size_t)cols);
+        const float4 b0 = *reinterpret_cast<const float4*>(bias + c), b1 = *reinterpret_cast<const float4*>(bias + c + 4);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+        float f[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 t = __bfloat1622float2(h[e]); f[2 * e] = t.x; f[2 * e + 1] = t.y; }
+        f[0] += b0.x; f[1] += b0.y; f[2] += b0.z; f[3] += b0.w; f[4] += b1.x; f[5] += b1.y; f[6] += b1.z; f[7] += b1.w;
+        if (act == 1) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { f[e] = fmaxf(f[e], 0.f); f[e] *= f[e]; }
+        }
+        uint4 o;
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) oh[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+        out[i] = o;
+    }
+}
+
 __global__ void softcap_kernel(float* __restrict__ z, size_t n, float cap) {
     for (size_t i = (size_t)blockIdx.x * NT + threadIdx.x; i < n; i += (size_t)gridDim.x * NT) z[i] = cap * tanhf(z[i] / cap);
 }
@@ -151,7 +174,9 @@ MI_EXPORT int mi_dual_rmsnorm_mix(const void* a, const float* wa, float sa, cons
 MI_EXPORT int mi_bias_act(const void* z, const float* bias, void* out, long long rows, int cols, int act, int dtype, cudaStream_t stream) {
     const long long n = rows * cols;
     if (n == 0) return 0;
-    if (dtype == MI_BF16) bias_act_kernel<__nv_bfloat16><<<blocks_for(n), NT, 0, stream>>>((const __nv_bfloat16*)z, bias, (__nv_bfloat16*)out, (size_t)n, cols, act);
+    if (dtype == MI_BF16 && cols % 8 == 0 && (uintptr_t)z % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)bias % 16 == 0)
+        bias_act_vec_kernel<<<blocks_for(n / 8), NT, 0, stream>>>((const uint4*)z, bias, (uint4*)out, (size_t)(n / 8), cols, act);
+    else if (dtype == MI_BF16) bias_act_kernel<__nv_bfloat16><<<blocks_for(n), NT, 0, stream>>>((const __nv_bfloat16*)z, bias, (__nv_bfloat16*)out, (size_t)n, cols, act);
     else bias_act_kernel<float><<<blocks_for(n), NT, 0, stream>>>((const float*)z, bias, (float*)out, (size_t)n, cols, act);
     return (int)cudaGetLastError();
 }

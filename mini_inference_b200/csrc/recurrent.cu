@@ -442,6 +442,72 @@ __global__ void short_conv_kernel(const T* __restrict__ h, int ldh, const float*
     }
 }
 
+// The same for bfloat16 rows whose channels come in multiples of eight: a thread owns eight channels (16-byte loads and stores), keeps
+// their TAPS weights in registers and walks `tok` neighbouring tokens (each looks its own entry up: an entry may end between them).
+template <int TAPS>
+__global__ void short_conv_vec_kernel(const __nv_bfloat16* __restrict__ h, int ldh, const float* __restrict__ w, const float* __restrict__ bias,
+                                      const float* __restrict__ state, long long state_stride, long long hist_off, __nv_bfloat16* __restrict__ out,
+                                      const int* __restrict__ token_seg, const int* __restrict__ seg_q_start, const int* __restrict__ seg_slot,
+                                      int T_, int C, int residual, int act, int tok) {
+    // the block's weights pass through shared memory: read from w in order, then each thread takes its own 8 TAPS numbers
+    // (rows of 8 TAPS + 1 floats keep the threads on different banks)
+    constexpr int ROW = 8 * TAPS + 1;
+    __shared__ float wsm[256 * ROW];
+    const int cb = blockIdx.y * blockDim.x * 8;                                   // the block's first channel
+    const int mine = min((int)blockDim.x * 8, C - cb) * TAPS;
+    for (int i = threadIdx.x; i < mine; i += blockDim.x) wsm[(i / (8 * TAPS)) * ROW + i % (8 * TAPS)] = w[(size_t)cb * TAPS + i];
+    __syncthreads();
+    const int c = cb + threadIdx.x * 8;
+    if (c >= C) return;
+    float wreg[8][TAPS], breg[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) wreg[e][j] = wsm[threadIdx.x * ROW + e * TAPS + j];
+    }
+    if (bias) {
+        const float4 a = *reinterpret_cast<const float4*>(bias + c), b = *reinterpret_cast<const float4*>(bias + c + 4);
+        breg[0] = a.x; breg[1] = a.y; breg[2] = a.z; breg[3] = a.w; breg[4] = b.x; breg[5] = b.y; breg[6] = b.z; breg[7] = b.w;
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) breg[e] = 0.f;
+    }
+    const int t0 = blockIdx.x * tok;
+    for (int t = t0; t < min(t0 + tok, T_); ++t) {
+        const int seg = token_seg[t], qs = seg_q_start[seg], r = t - qs;
+        const float* hist = TAPS > 1 ? state + (long long)seg_slot[seg] * state_stride + hist_off : nullptr;
+        float acc[8], x[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = breg[e];
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) {
+            const int off = r - (TAPS - 1 - j);
+            if (off >= 0) {
+                const uint4 v = *reinterpret_cast<const uint4*>(h + (size_t)(qs + off) * ldh + c);
+                const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(hp[e]); x[2 * e] = f.x; x[2 * e + 1] = f.y; }
+            } else {
+                const float* hr = hist + (size_t)(TAPS - 1 + off) * C + c;
+                const float4 a = *reinterpret_cast<const float4*>(hr), b = *reinterpret_cast<const float4*>(hr + 4);
+                x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] = fmaf(wreg[e][j], x[e], acc[e]);
+        }
+        uint4 o;
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            if (act == 1) acc[e] = silu(acc[e]);
+            if (residual) acc[e] += x[e];                    // x holds the last tap's input: the token's own
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) oh[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+        *reinterpret_cast<uint4*>(out + (size_t)t * C + c) = o;
+    }
+}
+
 // ------------------------------------------------------------------ general delta rule, prologue
 // p [T, ldp] = r | k | v | a | g | low (H D, H D, H V, H D, H V, rank columns).  A block takes TOK neighbouring tokens and a
 // range of channels: low = tanh(.), decay = exp(-decay_scale sigmoid(w2 low + w0)) with w2 [H D, rank] read once for the
@@ -476,10 +542,27 @@ __global__ void __launch_bounds__(256) general_delta_prepare_kernel(const T* __r
 #pragma unroll
         for (int k = 0; k < TOK; ++k) acc[k] = 0.f;
         const T* wr = w2 + (size_t)i * rank;
-        for (int j = 0; j < rank; ++j) {
-            const float wv = to_f32(wr[j]);
+        if (sizeof(T) == 2 && rank % 8 == 0 && (uintptr_t)w2 % 16 == 0) {
+            // a row of w2 is read sixteen bytes at a time: a warp's 32 rows are 32 cache lines, each used whole
+            for (int j = 0; j < rank; j += 8) {
+                const uint4 v = *reinterpret_cast<const uint4*>(wr + j);
+                const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(&v);
+                const float2 w01 = __bfloat1622float2(hp[0]), w23 = __bfloat1622float2(hp[1]), w45 = __bfloat1622float2(hp[2]), w67 = __bfloat1622float2(hp[3]);
 #pragma unroll
-            for (int k = 0; k < TOK; ++k) acc[k] = fmaf(low_s[k * rank + j], wv, acc[k]);
+                for (int k = 0; k < TOK; ++k) {                  // the token's eight inputs in two 16-byte reads (every thread the same address)
+                    const float4 la = *reinterpret_cast<const float4*>(low_s + k * rank + j), lb = *reinterpret_cast<const float4*>(low_s + k * rank + j + 4);
+                    float a = acc[k];
+                    a = fmaf(la.x, w01.x, a); a = fmaf(la.y, w01.y, a); a = fmaf(la.z, w23.x, a); a = fmaf(la.w, w23.y, a);
+                    a = fmaf(lb.x, w45.x, a); a = fmaf(lb.y, w45.y, a); a = fmaf(lb.z, w67.x, a); a = fmaf(lb.w, w67.y, a);
+                    acc[k] = a;
+                }
+            }
+        } else {
+            for (int j = 0; j < rank; ++j) {
+                const float wv = to_f32(wr[j]);
+#pragma unroll
+                for (int k = 0; k < TOK; ++k) acc[k] = fmaf(low_s[k * rank + j], wv, acc[k]);
+            }
         }
         const float b0 = w0[i], ab = a_b[i];
         const int hh = i / D;
@@ -515,24 +598,37 @@ __global__ void memory_gates_kernel(const float* __restrict__ gl, const float* _
     lg[idx] = z;
 }
 
-// (2) per (entry, head), in order: m' = max(f + m, i) from the slot's m; lg becomes [f + m - m' | i - m'] and mneg = -m'
+// (2) per (entry, head), in order: m' = max(f + m, i) from the slot's m; lg becomes [f + m - m' | i - m'] and mneg = -m'.
+// m -> max(m + f, i) composes: first (F1, I1), then (F2, I2) is (F1 + F2, max(I1 + F2, I2)).  A warp takes a head and scans 32 tokens at a
+// time with shuffles, carrying m from one group of 32 to the next.
 __global__ void memory_max_kernel(float* __restrict__ lg, float* __restrict__ mneg, float* __restrict__ state, long long state_stride,
                                   long long m_off, const int* __restrict__ seg_q_start, const int* __restrict__ seg_slot, int H) {
     const int seg = blockIdx.x, qs = seg_q_start[seg], n = seg_q_start[seg + 1] - qs;
+    const int lane = threadIdx.x & 31, h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (h >= H) return;
     float* ms = state + (long long)seg_slot[seg] * state_stride + m_off;
-    for (int h = threadIdx.x; h < H; h += blockDim.x) {
-        float m = ms[h];
-#pragma unroll 4
-        for (int t = qs; t < qs + n; ++t) {
-            const float i = lg[(size_t)t * 2 * H + h], f = lg[(size_t)t * 2 * H + H + h];
-            const float mn = fmaxf(f + m, i);
-            lg[(size_t)t * 2 * H + h] = i - mn;
-            lg[(size_t)t * 2 * H + H + h] = f + m - mn;
-            mneg[(size_t)t * H + h] = -mn;
-            m = mn;
+    float m = ms[h];
+    for (int base = 0; base < n; base += 32) {
+        const bool ok = base + lane < n;
+        const size_t t = (size_t)qs + base + lane;
+        const float i = ok ? lg[t * 2 * H + h] : -INFINITY, f = ok ? lg[t * 2 * H + H + h] : 0.f;
+        float F = f, I = i;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const float Fp = __shfl_up_sync(0xffffffffu, F, d), Ip = __shfl_up_sync(0xffffffffu, I, d);
+            if (lane >= d) { I = fmaxf(Ip + F, I); F += Fp; }
         }
-        ms[h] = m;
+        const float mn = fmaxf(m + F, I);                       // the maximum after this lane's token
+        float before = __shfl_up_sync(0xffffffffu, mn, 1);
+        if (lane == 0) before = m;
+        if (ok) {
+            lg[t * 2 * H + h] = i - mn;
+            lg[t * 2 * H + H + h] = f + before - mn;
+            mneg[t * H + h] = -mn;
+        }
+        m = __shfl_sync(0xffffffffu, mn, min(31, n - base - 1));
     }
+    if (lane == 0) ms[h] = m;
 }
 
 // (3) per token: what the scan stages, float32: q * q_scale | e^(i - m') k | per head [v, 1, 0, 0, 0] | e^(f + m - m') per head
@@ -590,6 +686,7 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(const T* __restrict
     float* st = Cs + SS_TC * N;             // [SS_TC][32] step
     float* xs = st + SS_TC * 32;            // [SS_TC][32]
     float* zs = xs + SS_TC * 32;            // [SS_TC][32]
+    float* ys = zs + SS_TC * 32;            // [SS_TC][32] the read-outs of a chunk, finished after the chunk's tokens
     const int seg = blockIdx.x, qs = seg_q_start[seg], n = seg_q_start[seg + 1] - qs;
     const int c0 = blockIdx.y * 32, cl = threadIdx.x >> 3, l = threadIdx.x & 7, c = c0 + cl;
     const bool live = c < I;
@@ -602,28 +699,57 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(const T* __restrict
         s[g] = ok ? S[nn] : 0.f;
         a[g] = ok ? A[(size_t)c * N + nn] : 0.f;
     }
-    const float dv = live ? Dv[c] : 0.f;
+    // a chunk's inputs are fetched into registers while the chunk before it is computed, and stored to shared memory after it
+    constexpr int RB = (SS_TC * 8 * NG + 255) / 256;
+    float rB[RB], rC[RB], rs[2], rx[2], rz[2];
+    auto fetch = [&](int t0) {
+        const int nt = min(SS_TC, n - t0);
+#pragma unroll
+        for (int r = 0; r < RB; ++r) {
+            const int i = threadIdx.x + 256 * r;
+            if (i < nt * N) {
+                const int tt = i / N, nn = i - tt * N;
+                rB[r] = to_f32(B[(size_t)(qs + t0 + tt) * ldb + nn]);
+                rC[r] = to_f32(Cm[(size_t)(qs + t0 + tt) * ldc + nn]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int i = threadIdx.x + 256 * r, tt = i >> 5, cc = c0 + (i & 31);
+            if (tt < nt && cc < I) {
+                const size_t tok = qs + t0 + tt;
+                rs[r] = dt[tok * I + cc] + dt_b[cc];
+                rx[r] = to_f32(x[tok * I + cc]);
+                rz[r] = to_f32(z[tok * ldz + cc]);
+            }
+        }
+    };
+    static_assert(SS_TC * 32 <= 2 * 256, "two step / input / gate values a thread");
+    if (n > 0) fetch(0);
     for (int t0 = 0; t0 < n; t0 += SS_TC) {
         const int nt = min(SS_TC, n - t0);
         __syncthreads();
-        for (int i = threadIdx.x; i < nt * N; i += 256) {
-            const int tt = i / N, nn = i - tt * N;
-            Bs[i] = to_f32(B[(size_t)(qs + t0 + tt) * ldb + nn]);
-            Cs[i] = to_f32(Cm[(size_t)(qs + t0 + tt) * ldc + nn]);
+#pragma unroll
+        for (int r = 0; r < RB; ++r) {
+            const int i = threadIdx.x + 256 * r;
+            if (i < nt * N) { Bs[i] = rB[r]; Cs[i] = rC[r]; }
         }
-        for (int i = threadIdx.x; i < nt * 32; i += 256) {
-            const int tt = i >> 5, cc = c0 + (i & 31);
-            if (cc < I) {
-                const size_t tok = qs + t0 + tt;
-                const float v = dt[tok * I + cc] + dt_b[cc];
-                st[i] = v > 20.f ? v : log1pf(expf(v));
-                xs[i] = to_f32(x[tok * I + cc]);
-                zs[i] = to_f32(z[tok * ldz + cc]);
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int i = threadIdx.x + 256 * r, tt = i >> 5, cc = c0 + (i & 31);
+            if (tt < nt && cc < I) {
+                st[i] = rs[r] > 20.f ? rs[r] : log1pf(expf(rs[r]));
+                xs[i] = rx[r];
+                zs[i] = rz[r];
             }
         }
         __syncthreads();
+        if (t0 + SS_TC < n) fetch(t0 + SS_TC);
+        // only the state's own update is a chain from token to token: the exponentials, the read-out's sum over the states and
+        // its reduction over the eight lanes of a channel overlap between neighbouring tokens once the loop is unrolled
+#pragma unroll 4
         for (int tt = 0; tt < nt; ++tt) {
-            const float step = st[tt * 32 + cl], xv = xs[tt * 32 + cl], sx = step * xv;
+            const float step = st[tt * 32 + cl], sx = step * xs[tt * 32 + cl];
             float y = 0.f;
 #pragma unroll
             for (int g = 0; g < NG; ++g) {
@@ -636,7 +762,13 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(const T* __restrict
             y += __shfl_xor_sync(0xffffffffu, y, 1);
             y += __shfl_xor_sync(0xffffffffu, y, 2);
             y += __shfl_xor_sync(0xffffffffu, y, 4);
-            if (l == 0 && live) out[(size_t)(qs + t0 + tt) * I + c] = from_f32<T>((y + dv * xv) * silu(zs[tt * 32 + cl]));
+            if (l == 0) ys[tt * 32 + cl] = y;
+        }
+        __syncthreads();
+        // skip term, gate and store for the whole chunk: a warp writes 32 neighbouring channels of one token
+        for (int i = threadIdx.x; i < nt * 32; i += 256) {
+            const int tt = i >> 5, cc = c0 + (i & 31);
+            if (cc < I) out[(size_t)(qs + t0 + tt) * I + cc] = from_f32<T>((ys[i] + Dv[cc] * xs[i]) * silu(zs[i]));
         }
     }
 #pragma unroll
@@ -720,7 +852,16 @@ MI_EXPORT int mi_short_conv(const void* h, int ldh, const float* w, const float*
                             int residual, int act, int dtype, cudaStream_t stream) {
     if (T_ == 0) return 0;
     dim3 grid(T_, T_ >= 256 ? 1 : min(8, (C + 255) / 256));
-    if (dtype == MI_BF16)
+    const bool vec = dtype == MI_BF16 && taps >= 1 && taps <= 4 && C % 8 == 0 && ldh % 8 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+                     (taps == 1 || (state_stride % 4 == 0 && hist_off % 4 == 0 && (uintptr_t)state % 16 == 0)) && (!bias || (uintptr_t)bias % 16 == 0);
+    if (vec) {
+        const int tok = T_ >= 1024 ? 4 : 1, threads = min(256, (C / 8 + 31) / 32 * 32);
+        dim3 vgrid((T_ + tok - 1) / tok, (C / 8 + threads - 1) / threads);
+#define GO(TAPS) short_conv_vec_kernel<TAPS><<<vgrid, threads, 0, stream>>>((const __nv_bfloat16*)h, ldh, w, bias, state, state_stride, hist_off, \
+                     (__nv_bfloat16*)out, token_seg, seg_q_start, seg_slot, T_, C, residual, act, tok)
+        if (taps == 1) GO(1); else if (taps == 2) GO(2); else if (taps == 3) GO(3); else GO(4);
+#undef GO
+    } else if (dtype == MI_BF16)
         short_conv_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)h, ldh, w, bias, state, state_stride, hist_off, (__nv_bfloat16*)out,
                                                                     token_seg, seg_q_start, seg_slot, C, taps, residual, act);
     else
@@ -770,7 +911,7 @@ MI_EXPORT int mi_matrix_memory(const void* p, int ldp, const float* gl, const fl
     const int W = V + 4, HD = H * D, n = T_ * 2 * H;
     if (H > 65535) return -2;
     memory_gates_kernel<<<(n + 255) / 256, 256, 0, stream>>>(gl, gate_bias, lg, n, H, cap, capped);
-    memory_max_kernel<<<num_segs, min(256, (H + 31) / 32 * 32), 0, stream>>>(lg, mneg, state, state_stride, (long long)HD * W, seg_q_start, seg_slot, H);
+    memory_max_kernel<<<dim3(num_segs, (H + 7) / 8), 256, 0, stream>>>(lg, mneg, state, state_stride, (long long)HD * W, seg_q_start, seg_slot, H);
     const float q_scale = 1.f / sqrtf((float)D);
     if (dtype == MI_BF16) memory_prepare_kernel<__nv_bfloat16><<<T_, 256, 0, stream>>>((const __nv_bfloat16*)p, ldp, lg, prep, ldprep, H, D, V, q_scale);
     else memory_prepare_kernel<float><<<T_, 256, 0, stream>>>((const float*)p, ldp, lg, prep, ldprep, H, D, V, q_scale);
@@ -794,7 +935,7 @@ MI_EXPORT int mi_selective_scan(const void* x, const float* dt, const float* dt_
     if (T_ == 0 || num_segs == 0) return 0;
     if (N > 128) return -2;
     const int NG = (N + 7) / 8;
-    const size_t smem = (size_t)SS_TC * (2 * N + 96) * sizeof(float);
+    const size_t smem = (size_t)SS_TC * (2 * N + 128) * sizeof(float);
     dim3 grid(num_segs, (I + 31) / 32);
     if (grid.y > 65535) return -2;
 #define GO(T, G) selective_scan_kernel<T, G><<<grid, 256, smem, stream>>>((const T*)x, dt, dt_b, A, (const T*)B, ldb, (const T*)C, ldc, Dv, (const T*)z, ldz, \

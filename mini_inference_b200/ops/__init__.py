@@ -883,8 +883,8 @@ class CudaOps:
             return out
         reach = meta.max_kv_len if not blk else min(meta.max_kv_len, blk)              # the most keys a decoded token can see
         reach = reach if not win else min(reach, win)
-        if (plain and self.fast_attention and q.dtype == torch.bfloat16 and D == V and D in (64, 128) and H // KV <= 16 and meta.page_size % 16 == 0
-                and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
+        if ((plain or self.biased_attention_tc) and self.fast_attention and q.dtype == torch.bfloat16 and D == V and D in (64, 128) and H // KV <= 16
+                and meta.page_size % 16 == 0 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
             # the tensor-core decode kernel (the G query heads of a kv head are the rows of one tile), split weights
             S = self.choose_splits(num_decode * KV, reach, 2 if self.bulk_decode else 3, cluster=self.bulk_decode and self.cluster_merge, head_dim=D)
             o_part = lse = counters = None
@@ -896,11 +896,16 @@ class CudaOps:
                         raise ValueError(f"attn_decode: {num_decode} rows x {KV} kv heads exceed the {self._merge_counters.numel()} "
                                          "merge counters allocated at start-up")
                     counters = self._merge_counters
-            _check(self.lib.mi_attn_decode_mma_rows_masked(
-                _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(o_part), _p(lse), _p(meta.decode_segs), num_decode,
-                _p(meta.seg_q_start), _p(meta.seg_kv_len), _p(meta.block_table), _p(rows), meta.max_pages, H, KV, D, meta.page_size, S,
-                _c.c_float(scale), win, _p(counters), _p(self._stream_error if self.bulk_decode else None), k_cache.shape[0],
-                int(self.cluster_merge and counters is not None), blk, int(bool(sink)), self._stream()), "attn_decode_mma_masked")
+            args = (_p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(o_part), _p(lse), _p(meta.decode_segs), num_decode,
+                    _p(meta.seg_q_start), _p(meta.seg_kv_len), _p(meta.block_table), _p(rows), meta.max_pages, H, KV, D, meta.page_size, S,
+                    _c.c_float(scale), win, _p(counters), _p(self._stream_error if self.bulk_decode else None), k_cache.shape[0],
+                    int(self.cluster_merge and counters is not None), blk, int(bool(sink)))
+            if plain:
+                _check(self.lib.mi_attn_decode_mma_rows_masked(*args, self._stream()), "attn_decode_mma_masked")
+            else:                                          # the learned sink's score and the distance table (one row per head) in the softmax
+                bias_t = self._bias_rows_by_head(distance_bias, distance_bias_by_head, H, q.device)
+                _check(self.lib.mi_attn_decode_mma_rows_biased(*args, _p(sink_values), _p(bias_t), bias_t.shape[1] - 1, self._stream()),
+                       "attn_decode_mma_biased")
             self.launches += 1
             if S > 1 and counters is None:
                 _check(self.lib.mi_attn_decode_merge(_p(o_part), _p(lse), _p(out), _p(meta.decode_segs), num_decode,

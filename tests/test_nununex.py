@@ -772,14 +772,16 @@ def test_kernels_against_the_stand_ins(dtype, lens, slots, starts):
     lo = f32(7, 131) * 40
     assert close(ops.softcap(lo.clone().to(dev), 25.0), ref.softcap(lo, 25.0), 1e-6)
     # the filter: one to five taps, a strided view as input, the state behind an offset, with and without bias, activation, residual
-    for C, taps, off in ((48, 4, 0), (77, 2, 5), (192, 3, 192 * 7), (33, 5, 1), (20, 1, 0)):
-        wide, w, b = rnd(T, C + 9), f32(C, taps), f32(C)
-        st = f32(5, off + (taps - 1) * C + 3)
+    # (rows that start on a 16-byte boundary with channels in eights take the kernel that moves eight channels a thread)
+    for C, taps, off, lead, more in ((48, 4, 0, 4, 9), (48, 4, 0, 8, 8), (77, 2, 5, 4, 9), (192, 3, 192 * 7, 4, 9), (192, 3, 192 * 7, 16, 16), (33, 5, 1, 4, 9),
+                                     (20, 1, 0, 4, 9), (2048, 2, 8, 0, 0), (40, 1, 0, 8, 8), (64, 5, 4, 0, 8)):
+        wide, w, b = rnd(T, C + more), f32(C, taps), f32(C)
+        st = f32(5, off + (taps - 1) * C + (4 if lead % 8 == 0 else 3))
         for bias, residual, act in ((None, True, "none"), (b, False, "silu"), (b, True, "none")):
             sa, sb = st.clone().to(dev), st.clone()
-            ya = ops.short_conv(wide.to(dev)[:, 4:4 + C], w.to(dev), None if bias is None else bias.to(dev), taps, sa, off, dbatch, residual, act)
-            yb = ref.short_conv(wide[:, 4:4 + C], w, bias, taps, sb, off, batch, residual, act)
-            assert close(ya, yb) and close(sa, sb, 1e-6), (C, taps)
+            ya = ops.short_conv(wide.to(dev)[:, lead:lead + C], w.to(dev), None if bias is None else bias.to(dev), taps, sa, off, dbatch, residual, act)
+            yb = ref.short_conv(wide[:, lead:lead + C], w, bias, taps, sb, off, batch, residual, act)
+            assert close(ya, yb) and close(sa, sb, 1e-6), (C, taps, lead)
     # the general delta rule
     for H, D, V, rank in ((3, 8, 8, 5), (1, 20, 20, 1), (2, 64, 64, 16), (3, 5, 5, 2), (2, 33, 33, 7), (1, 128, 128, 32)):
         HD = H * D
