@@ -443,12 +443,22 @@ __global__ void short_conv_kernel(const T* __restrict__ h, int ldh, const float*
 }
 
 // The same for bfloat16 rows whose channels come in multiples of eight: a thread owns eight channels (16-byte loads and stores), keeps
-// their TAPS weights in registers and walks `tok` neighbouring tokens (each looks its own entry up: an entry may end between them).
-template <int TAPS>
+// their TAPS weights in registers and walks TOK neighbouring tokens (each looks its own entry up: an entry may end between them).
+template <int TAPS, int TOK>
 __global__ void short_conv_vec_kernel(const __nv_bfloat16* __restrict__ h, int ldh, const float* __restrict__ w, const float* __restrict__ bias,
                                       const float* __restrict__ state, long long state_stride, long long hist_off, __nv_bfloat16* __restrict__ out,
                                       const int* __restrict__ token_seg, const int* __restrict__ seg_q_start, const int* __restrict__ seg_slot,
-                                      int T_, int C, int residual, int act, int tok) {
+                                      int T_, int C, int residual, int act) {
+    // where each of the block's tokens stands in its entry: looked up first, all at once, so that the chains of dependent reads
+    // (token -> entry -> start and slot) run side by side and under the staging of the weights
+    const int t0 = blockIdx.x * TOK;
+    int qs_[TOK], slot_[TOK];
+#pragma unroll
+    for (int k = 0; k < TOK; ++k) {
+        const int seg = token_seg[min(t0 + k, T_ - 1)];
+        qs_[k] = seg_q_start[seg];
+        slot_[k] = seg_slot[seg];
+    }
     // the block's weights pass through shared memory: read from w in order, then each thread takes its own 8 TAPS numbers
     // (rows of 8 TAPS + 1 floats keep the threads on different banks)
     constexpr int ROW = 8 * TAPS + 1;
@@ -472,10 +482,12 @@ __global__ void short_conv_vec_kernel(const __nv_bfloat16* __restrict__ h, int l
 #pragma unroll
         for (int e = 0; e < 8; ++e) breg[e] = 0.f;
     }
-    const int t0 = blockIdx.x * tok;
-    for (int t = t0; t < min(t0 + tok, T_); ++t) {
-        const int seg = token_seg[t], qs = seg_q_start[seg], r = t - qs;
-        const float* hist = TAPS > 1 ? state + (long long)seg_slot[seg] * state_stride + hist_off : nullptr;
+#pragma unroll
+    for (int k = 0; k < TOK; ++k) {
+        const int t = t0 + k;
+        if (t >= T_) break;
+        const int qs = qs_[k], r = t - qs;
+        const float* hist = TAPS > 1 ? state + (long long)slot_[k] * state_stride + hist_off : nullptr;
         float acc[8], x[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[e] = breg[e];
@@ -701,7 +713,8 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(const T* __restrict
     }
     // a chunk's inputs are fetched into registers while the chunk before it is computed, and stored to shared memory after it
     constexpr int RB = (SS_TC * 8 * NG + 255) / 256;
-    float rB[RB], rC[RB], rs[2], rx[2], rz[2];
+    T rB[RB], rC[RB], rx[2], rz[2];             // as loaded: converting here would wait for the load
+    float rs[2], rb[2];
     auto fetch = [&](int t0) {
         const int nt = min(SS_TC, n - t0);
 #pragma unroll
@@ -709,8 +722,8 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(const T* __restrict
             const int i = threadIdx.x + 256 * r;
             if (i < nt * N) {
                 const int tt = i / N, nn = i - tt * N;
-                rB[r] = to_f32(B[(size_t)(qs + t0 + tt) * ldb + nn]);
-                rC[r] = to_f32(Cm[(size_t)(qs + t0 + tt) * ldc + nn]);
+                rB[r] = B[(size_t)(qs + t0 + tt) * ldb + nn];
+                rC[r] = Cm[(size_t)(qs + t0 + tt) * ldc + nn];
             }
         }
 #pragma unroll
@@ -718,9 +731,10 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(const T* __restrict
             const int i = threadIdx.x + 256 * r, tt = i >> 5, cc = c0 + (i & 31);
             if (tt < nt && cc < I) {
                 const size_t tok = qs + t0 + tt;
-                rs[r] = dt[tok * I + cc] + dt_b[cc];
-                rx[r] = to_f32(x[tok * I + cc]);
-                rz[r] = to_f32(z[tok * ldz + cc]);
+                rs[r] = dt[tok * I + cc];
+                rb[r] = dt_b[cc];
+                rx[r] = x[tok * I + cc];
+                rz[r] = z[tok * ldz + cc];
             }
         }
     };
@@ -732,15 +746,16 @@ __global__ void __launch_bounds__(256) selective_scan_kernel(const T* __restrict
 #pragma unroll
         for (int r = 0; r < RB; ++r) {
             const int i = threadIdx.x + 256 * r;
-            if (i < nt * N) { Bs[i] = rB[r]; Cs[i] = rC[r]; }
+            if (i < nt * N) { Bs[i] = to_f32(rB[r]); Cs[i] = to_f32(rC[r]); }
         }
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             const int i = threadIdx.x + 256 * r, tt = i >> 5, cc = c0 + (i & 31);
             if (tt < nt && cc < I) {
-                st[i] = rs[r] > 20.f ? rs[r] : log1pf(expf(rs[r]));
-                xs[i] = rx[r];
-                zs[i] = rz[r];
+                const float v = rs[r] + rb[r];
+                st[i] = v > 20.f ? v : log1pf(expf(v));
+                xs[i] = to_f32(rx[r]);
+                zs[i] = to_f32(rz[r]);
             }
         }
         __syncthreads();
@@ -852,14 +867,17 @@ MI_EXPORT int mi_short_conv(const void* h, int ldh, const float* w, const float*
                             int residual, int act, int dtype, cudaStream_t stream) {
     if (T_ == 0) return 0;
     dim3 grid(T_, T_ >= 256 ? 1 : min(8, (C + 255) / 256));
-    const bool vec = dtype == MI_BF16 && taps >= 1 && taps <= 4 && C % 8 == 0 && ldh % 8 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+    // prompt portions only: a decode step's few tokens are done sooner by the kernel that needs no staging of weights
+    const bool vec = dtype == MI_BF16 && T_ >= 256 && taps >= 1 && taps <= 4 && C % 8 == 0 && ldh % 8 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)out % 16 == 0 &&
                      (taps == 1 || (state_stride % 4 == 0 && hist_off % 4 == 0 && (uintptr_t)state % 16 == 0)) && (!bias || (uintptr_t)bias % 16 == 0);
     if (vec) {
-        const int tok = T_ >= 1024 ? 4 : 1, threads = min(256, (C / 8 + 31) / 32 * 32);
+        const int tok = T_ >= 1024 ? 8 : 2, threads = min(256, (C / 8 + 31) / 32 * 32);
         dim3 vgrid((T_ + tok - 1) / tok, (C / 8 + threads - 1) / threads);
-#define GO(TAPS) short_conv_vec_kernel<TAPS><<<vgrid, threads, 0, stream>>>((const __nv_bfloat16*)h, ldh, w, bias, state, state_stride, hist_off, \
-                     (__nv_bfloat16*)out, token_seg, seg_q_start, seg_slot, T_, C, residual, act, tok)
-        if (taps == 1) GO(1); else if (taps == 2) GO(2); else if (taps == 3) GO(3); else GO(4);
+#define GO(TAPS, TOK) short_conv_vec_kernel<TAPS, TOK><<<vgrid, threads, 0, stream>>>((const __nv_bfloat16*)h, ldh, w, bias, state, state_stride, hist_off, \
+                          (__nv_bfloat16*)out, token_seg, seg_q_start, seg_slot, T_, C, residual, act)
+#define PICK(TAPS) do { if (tok == 8) GO(TAPS, 8); else GO(TAPS, 2); } while (0)
+        if (taps == 1) PICK(1); else if (taps == 2) PICK(2); else if (taps == 3) PICK(3); else PICK(4);
+#undef PICK
 #undef GO
     } else if (dtype == MI_BF16)
         short_conv_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)h, ldh, w, bias, state, state_stride, hist_off, (__nv_bfloat16*)out,
