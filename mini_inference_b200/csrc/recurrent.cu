@@ -425,20 +425,28 @@ template <typename T>
 __global__ void short_conv_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w, const float* __restrict__ bias,
                                   const float* __restrict__ state, long long state_stride, long long hist_off, T* __restrict__ out,
                                   const int* __restrict__ token_seg, const int* __restrict__ seg_q_start, const int* __restrict__ seg_slot,
-                                  int C, int taps, int residual, int act) {
+                                  int C, int taps, int residual, int act, int shift) {
+    // shift != 0 (every entry of the step brings ONE token, so a channel of a slot has one reader): the thread also moves the
+    // slot's inputs up by one and appends the token's own, which conv_tail_kernel does for steps of any other shape
     const int t = blockIdx.x, seg = token_seg[t], qs = seg_q_start[seg], r = t - qs;
     const float* hist = taps > 1 ? state + (long long)seg_slot[seg] * state_stride + hist_off : nullptr;
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
         float acc = 0.f;
+        const float own = to_f32(h[(size_t)t * ldh + c]);
         for (int j = 0; j < taps; ++j) {
             const int off = r - (taps - 1 - j);
-            const float x = off >= 0 ? to_f32(h[(size_t)(qs + off) * ldh + c]) : hist[(size_t)(taps - 1 + off) * C + c];
+            const float x = j == taps - 1 ? own : off >= 0 ? to_f32(h[(size_t)(qs + off) * ldh + c]) : hist[(size_t)(taps - 1 + off) * C + c];
             acc = fmaf(w[(size_t)c * taps + j], x, acc);
         }
         if (bias) acc += bias[c];
         if (act == 1) acc = silu(acc);
-        if (residual) acc += to_f32(h[(size_t)t * ldh + c]);
+        if (residual) acc += own;
         out[(size_t)t * C + c] = from_f32<T>(acc);
+        if (shift && taps > 1) {
+            float* hw = const_cast<float*>(hist);
+            for (int j = 0; j + 2 < taps; ++j) hw[(size_t)j * C + c] = hw[(size_t)(j + 1) * C + c];
+            hw[(size_t)(taps - 2) * C + c] = own;
+        }
     }
 }
 
@@ -645,12 +653,7 @@ __global__ void memory_max_kernel(float* __restrict__ lg, float* __restrict__ mn
 
 // (3) per token: what the scan stages, float32: q * q_scale | e^(i - m') k | per head [v, 1, 0, 0, 0] | e^(f + m - m') per head
 template <typename T>
-__global__ void memory_prepare_kernel(const T* __restrict__ p, int ldp, const float* __restrict__ lg, float* __restrict__ out, int ldo,
-                                      int H, int D, int V, float q_scale) {
-    const size_t t = blockIdx.x;
-    const T* row = p + t * ldp;
-    float* o = out + t * ldo;
-    const float* g = lg + t * 2 * H;
+__device__ __forceinline__ void memory_prepare_row(const T* __restrict__ row, const float* __restrict__ g, float* __restrict__ o, int H, int D, int V, float q_scale) {
     const int HD = H * D, W = V + 4;
     for (int i = threadIdx.x; i < HD; i += blockDim.x) {
         o[i] = to_f32(row[i]) * q_scale;
@@ -661,6 +664,36 @@ __global__ void memory_prepare_kernel(const T* __restrict__ p, int ldp, const fl
         o[2 * HD + i] = c < V ? to_f32(row[2 * HD + hh * V + c]) : c == V ? 1.f : 0.f;
     }
     for (int hh = threadIdx.x; hh < H; hh += blockDim.x) o[2 * HD + H * W + hh] = expf(g[H + hh]);
+}
+
+template <typename T>
+__global__ void memory_prepare_kernel(const T* __restrict__ p, int ldp, const float* __restrict__ lg, float* __restrict__ out, int ldo,
+                                      int H, int D, int V, float q_scale) {
+    const size_t t = blockIdx.x;
+    memory_prepare_row(p + t * ldp, lg + t * 2 * H, out + t * ldo, H, D, V, q_scale);
+}
+
+// (1) - (3) in one kernel for a step in which every entry brings ONE token (decode steps): a block per entry
+template <typename T>
+__global__ void memory_step_kernel(const T* __restrict__ p, int ldp, const float* __restrict__ gl, const float* __restrict__ bias, float cap, int capped,
+                                   float* __restrict__ mneg, float* __restrict__ out, int ldo, float* __restrict__ state, long long state_stride,
+                                   long long m_off, const int* __restrict__ seg_q_start, const int* __restrict__ seg_slot, int H, int D, int V, float q_scale) {
+    extern __shared__ float gsh[];                          // [2 H]: i - m' | f + m - m'
+    const int seg = blockIdx.x;
+    const size_t t = seg_q_start[seg];
+    float* ms = state + (long long)seg_slot[seg] * state_stride + m_off;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        float zi = gl[t * 2 * H + h] + bias[h], zf = gl[t * 2 * H + H + h] + bias[H + h];
+        if (capped) { zi = cap * tanhf(zi / cap); zf = cap * tanhf(zf / cap); }
+        const float f = fminf(zf, 0.f) - log1pf(expf(-fabsf(zf)));          // logsigmoid
+        const float m = ms[h], mn = fmaxf(f + m, zi);
+        gsh[h] = zi - mn;
+        gsh[H + h] = f + m - mn;
+        mneg[t * H + h] = -mn;
+        ms[h] = mn;
+    }
+    __syncthreads();
+    memory_prepare_row(p + t * ldp, gsh, out + t * ldo, H, D, V, q_scale);
 }
 
 // (4) per (token, head): o = full[:V] / (max(|full[V]|, e^(-m)) + den_eps); rows = o / rms(o) * weight * sigmoid(gate)
@@ -867,6 +900,7 @@ MI_EXPORT int mi_short_conv(const void* h, int ldh, const float* w, const float*
                             int residual, int act, int dtype, cudaStream_t stream) {
     if (T_ == 0) return 0;
     dim3 grid(T_, T_ >= 256 ? 1 : min(8, (C + 255) / 256));
+    const int shift = (T_ == num_segs && T_ < 256) ? 1 : 0;      // a step of single tokens: one kernel filters and moves the slot's inputs
     // prompt portions only: a decode step's few tokens are done sooner by the kernel that needs no staging of weights
     const bool vec = dtype == MI_BF16 && T_ >= 256 && taps >= 1 && taps <= 4 && C % 8 == 0 && ldh % 8 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)out % 16 == 0 &&
                      (taps == 1 || (state_stride % 4 == 0 && hist_off % 4 == 0 && (uintptr_t)state % 16 == 0)) && (!bias || (uintptr_t)bias % 16 == 0);
@@ -881,12 +915,12 @@ MI_EXPORT int mi_short_conv(const void* h, int ldh, const float* w, const float*
 #undef GO
     } else if (dtype == MI_BF16)
         short_conv_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)h, ldh, w, bias, state, state_stride, hist_off, (__nv_bfloat16*)out,
-                                                                    token_seg, seg_q_start, seg_slot, C, taps, residual, act);
+                                                                    token_seg, seg_q_start, seg_slot, C, taps, residual, act, shift);
     else
         short_conv_kernel<float><<<grid, 256, 0, stream>>>((const float*)h, ldh, w, bias, state, state_stride, hist_off, (float*)out, token_seg,
-                                                            seg_q_start, seg_slot, C, taps, residual, act);
+                                                            seg_q_start, seg_slot, C, taps, residual, act, shift);
     int err = (int)cudaGetLastError();
-    if (err || taps <= 1) return err;
+    if (err || taps <= 1 || shift) return err;
     dim3 tgrid(num_segs, (C + 255) / 256);
     if (dtype == MI_BF16)
         conv_tail_kernel<__nv_bfloat16><<<tgrid, 256, 0, stream>>>((const __nv_bfloat16*)h, ldh, state, state_stride, hist_off, seg_q_start, seg_slot, C, taps);
@@ -928,11 +962,20 @@ MI_EXPORT int mi_matrix_memory(const void* p, int ldp, const float* gl, const fl
     if (T_ == 0) return 0;
     const int W = V + 4, HD = H * D, n = T_ * 2 * H;
     if (H > 65535) return -2;
-    memory_gates_kernel<<<(n + 255) / 256, 256, 0, stream>>>(gl, gate_bias, lg, n, H, cap, capped);
-    memory_max_kernel<<<dim3(num_segs, (H + 7) / 8), 256, 0, stream>>>(lg, mneg, state, state_stride, (long long)HD * W, seg_q_start, seg_slot, H);
     const float q_scale = 1.f / sqrtf((float)D);
-    if (dtype == MI_BF16) memory_prepare_kernel<__nv_bfloat16><<<T_, 256, 0, stream>>>((const __nv_bfloat16*)p, ldp, lg, prep, ldprep, H, D, V, q_scale);
-    else memory_prepare_kernel<float><<<T_, 256, 0, stream>>>((const float*)p, ldp, lg, prep, ldprep, H, D, V, q_scale);
+    if (T_ == num_segs && (size_t)2 * H * sizeof(float) <= 48 * 1024) {          // every entry brings one token: gates, maximum and prologue in one kernel
+        if (dtype == MI_BF16)
+            memory_step_kernel<__nv_bfloat16><<<num_segs, 256, 2 * H * sizeof(float), stream>>>((const __nv_bfloat16*)p, ldp, gl, gate_bias, cap, capped, mneg, prep, ldprep,
+                                                                                                 state, state_stride, (long long)HD * W, seg_q_start, seg_slot, H, D, V, q_scale);
+        else
+            memory_step_kernel<float><<<num_segs, 256, 2 * H * sizeof(float), stream>>>((const float*)p, ldp, gl, gate_bias, cap, capped, mneg, prep, ldprep, state, state_stride,
+                                                                                         (long long)HD * W, seg_q_start, seg_slot, H, D, V, q_scale);
+    } else {
+        memory_gates_kernel<<<(n + 255) / 256, 256, 0, stream>>>(gl, gate_bias, lg, n, H, cap, capped);
+        memory_max_kernel<<<dim3(num_segs, (H + 7) / 8), 256, 0, stream>>>(lg, mneg, state, state_stride, (long long)HD * W, seg_q_start, seg_slot, H);
+        if (dtype == MI_BF16) memory_prepare_kernel<__nv_bfloat16><<<T_, 256, 0, stream>>>((const __nv_bfloat16*)p, ldp, lg, prep, ldprep, H, D, V, q_scale);
+        else memory_prepare_kernel<float><<<T_, 256, 0, stream>>>((const float*)p, ldp, lg, prep, ldprep, H, D, V, q_scale);
+    }
     int err = (int)cudaGetLastError();
     if (err) return err;
     ScanLayout L{ldprep, 0, HD, 2 * HD, 0, 2 * HD + H * W, 0, 0};

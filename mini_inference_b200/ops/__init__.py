@@ -688,7 +688,7 @@ class CudaOps:
                                          _c.c_longlong(state.stride(0)), _c.c_longlong(H * D * V), _p(out), out.stride(0),
                                          _p(batch.token_seg), _p(batch.seg_q_start), _p(batch.seg_slot), T, batch.num_segs,
                                          H, KV, D, V, taps, _c.c_float(unit_eps), _code(p.dtype), self._stream()), "delta_prepare")
-        self.launches += 2 if taps > 1 else 1
+        self.launches += 2 if taps > 1 and not (T == batch.num_segs and T < 256) else 1
         return out
 
     def delta_scan(self, prep, H, KV, D, V, state, batch):
@@ -1144,7 +1144,7 @@ class CudaOps:
                                          _p(norm), _p(gate), gate.stride(0), _c.c_float(eps), _p(lg), _p(mneg), _p(prep), prep.stride(0), _p(full),
                                          _p(y), _p(state), _c.c_longlong(state.stride(0)), _p(batch.seg_q_start), _p(batch.seg_slot), T,
                                          batch.num_segs, H, D, V, _code(p.dtype), self._stream()), "matrix_memory")
-        self.launches += 5
+        self.launches += 3 if T == batch.num_segs else 5
         return y
 
     def selective_scan(self, x, dt, dt_b, A, B, C, Dv, z, state, batch, out_dtype):

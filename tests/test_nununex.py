@@ -729,7 +729,8 @@ def test_recurrences_remember_a_far_token_on_gpu():
 
 
 @gpu
-@pytest.mark.parametrize("lens,slots,starts", [([1, 23, 6, 2], [3, 1, 4, 2], [40, 0, 100, 0]), ([1000, 1, 59], [2, 4, 1], [0, 7, 300])])
+@pytest.mark.parametrize("lens,slots,starts", [([1, 23, 6, 2], [3, 1, 4, 2], [40, 0, 100, 0]), ([1000, 1, 59], [2, 4, 1], [0, 7, 300]),
+                                               ([1, 1, 1], [2, 4, 1], [5, 0, 9])])        # single tokens only: the step kernels
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_kernels_against_the_stand_ins(dtype, lens, slots, starts):
     """Every kernel of the design alone, at sizes no model above has (odd ones too), several entries of unequal length in one
