@@ -66,10 +66,12 @@ class ExecStep:
     cache this step's mixer reads instead of owning one.  add_row names a row of the model's
     table of pass vectors (ModelSpec.pass_vectors_name) that is added to the residual stream
     right before this step's layer runs (a model that repeats a span of layers marks each
-    repetition this way)."""
+    repetition this way).  add_embedding: the embedded tokens, as they entered the stream before the first
+    layer, are added to the stream right before this step's layer runs (row by row, in the stream's precision)."""
     layer: int
     cache_from: Optional[int] = None
     add_row: Optional[int] = None
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)
@@ -100,6 +102,9 @@ class ModelSpec:
     embedding_part_names: Tuple[Tuple[str, str], ...] = ()
     # logits <- cap * tanh(logits / cap) (None: the head's product as it is)
     logit_softcap: Optional[float] = None
+    # the embedded token is multiplied by embedding_scale as it enters a float32 stream; the head's product by logit_scale
+    embedding_scale: float = 1.0
+    logit_scale: float = 1.0
 
     def __post_init__(self):
         for i, step in enumerate(self.order):
@@ -112,5 +117,7 @@ class ModelSpec:
                     raise ValueError(f"order[{i}] reads the cache of step {step.cache_from}, which owns none")
             if step.add_row is not None and not 0 <= step.add_row < self.pass_vectors_rows:
                 raise ValueError(f"order[{i}] adds pass vector {step.add_row}; the model has {self.pass_vectors_rows}")
+            if step.add_row is not None and step.add_embedding:
+                raise ValueError(f"order[{i}] adds both a pass vector and the embedded tokens")
         if self.residual not in ("compute", "float32"):
             raise ValueError(f"residual '{self.residual}' is not one of compute, float32")

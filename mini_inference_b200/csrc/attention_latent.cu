@@ -22,13 +22,15 @@ constexpr int WARPS = 4;
 // q_out [T, H, C + R] = [q_abs | rotate(q rot part)];  cache row = [rmsnorm(dkv[:C]) * w | rotate(dkv[C:])].
 // Interleaved rotation: pairs (2i, 2i+1), i < nf, by the angle pos * inv_freq[i]; entries from 2 nf on pass unchanged.
 template <typename T>
-__global__ void latent_prepare_kernel(const T* __restrict__ p, int ldp, const T* __restrict__ q_abs, T* __restrict__ q_out,
+__global__ void latent_prepare_kernel(const T* __restrict__ p, int ldp, const T* __restrict__ q_rows, int ldq, int dkv_col,
+                                      const T* __restrict__ q_abs, T* __restrict__ q_out,
                                       T* __restrict__ cache, const float* __restrict__ norm_w, const float* __restrict__ inv_freq,
                                       int nf, const int* __restrict__ positions, const int* __restrict__ slots, int T_, int H,
                                       int D, int R, int C, float eps) {
     __shared__ float scratch[32];
     const int t = blockIdx.x;
     const T* row = p + (size_t)t * ldp;
+    const T* qrow = q_rows + (size_t)t * ldq;              // the query heads as projected: p itself, or a tensor of their own
     const float pos = (float)positions[t];
     T* qo = q_out + (size_t)t * H * (C + R);
     for (int idx = threadIdx.x; idx < H * C; idx += blockDim.x) {
@@ -37,7 +39,7 @@ __global__ void latent_prepare_kernel(const T* __restrict__ p, int ldp, const T*
     }
     for (int idx = threadIdx.x; idx < H * R; idx += blockDim.x) {
         const int h = idx / R, j = idx - h * R;
-        const T* src = row + (size_t)h * (D + R) + D;
+        const T* src = qrow + (size_t)h * (D + R) + D;
         float val = to_f32(src[j]);
         if (j < 2 * nf) {
             float sn, cs;
@@ -48,7 +50,7 @@ __global__ void latent_prepare_kernel(const T* __restrict__ p, int ldp, const T*
         qo[(size_t)h * (C + R) + C + j] = from_f32<T>(val);
     }
     if (cache == nullptr) return;
-    const T* dkv = row + (size_t)H * (D + R);
+    const T* dkv = row + dkv_col;
     float ss = 0.f;
     for (int i = threadIdx.x; i < C; i += blockDim.x) { const float v = to_f32(dkv[i]); ss += v * v; }
     const float r = rsqrtf(block_sum<128>(ss, scratch) / C + eps);
@@ -209,16 +211,21 @@ __global__ void latent_merge_kernel(const float* __restrict__ o_part, const floa
 
 }  // namespace
 
-MI_EXPORT int mi_latent_prepare(const void* p, int ldp, const void* q_abs, void* q_out, void* cache, const float* norm_w,
-                                const float* inv_freq, int nf, const int* positions, const int* slots, int T_, int H, int D, int R,
-                                int C, float eps, int dtype, cudaStream_t stream) {
+// q_rows (row stride ldq): where the query heads [H, D + R] as projected lie (null: at the start of p); dkv_col: the column of p
+// at which [c as projected | kr] starts (negative: behind the query heads, H (D + R)).
+MI_EXPORT int mi_latent_prepare(const void* p, int ldp, const void* q_rows, int ldq, int dkv_col, const void* q_abs, void* q_out, void* cache,
+                                const float* norm_w, const float* inv_freq, int nf, const int* positions, const int* slots, int T_, int H,
+                                int D, int R, int C, float eps, int dtype, cudaStream_t stream) {
     if (T_ == 0) return 0;
+    if (!q_rows) { q_rows = p; ldq = ldp; }
+    if (dkv_col < 0) dkv_col = H * (D + R);
     if (dtype == MI_BF16)
-        latent_prepare_kernel<__nv_bfloat16><<<T_, 128, 0, stream>>>((const __nv_bfloat16*)p, ldp, (const __nv_bfloat16*)q_abs, (__nv_bfloat16*)q_out,
+        latent_prepare_kernel<__nv_bfloat16><<<T_, 128, 0, stream>>>((const __nv_bfloat16*)p, ldp, (const __nv_bfloat16*)q_rows, ldq, dkv_col,
+                                                                     (const __nv_bfloat16*)q_abs, (__nv_bfloat16*)q_out,
                                                                      (__nv_bfloat16*)cache, norm_w, inv_freq, nf, positions, slots, T_, H, D, R, C, eps);
     else
-        latent_prepare_kernel<float><<<T_, 128, 0, stream>>>((const float*)p, ldp, (const float*)q_abs, (float*)q_out, (float*)cache, norm_w,
-                                                             inv_freq, nf, positions, slots, T_, H, D, R, C, eps);
+        latent_prepare_kernel<float><<<T_, 128, 0, stream>>>((const float*)p, ldp, (const float*)q_rows, ldq, dkv_col, (const float*)q_abs,
+                                                             (float*)q_out, (float*)cache, norm_w, inv_freq, nf, positions, slots, T_, H, D, R, C, eps);
     return (int)cudaGetLastError();
 }
 

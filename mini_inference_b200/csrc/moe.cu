@@ -3,7 +3,7 @@
 //
 //   route_topk   one block per token: logits = W_r h as float32 sums in a fixed order, s = softmax over all experts,
 //                choice scores c = s + correction; with groups, only experts of the `keep` groups (equal groups of
-//                neighbouring experts) whose largest c is largest stay eligible (the others count as -inf); the `top`
+//                neighbouring experts) whose largest c (or, as an option, the sum of whose two largest c) is largest stay eligible (the others count as -inf); the `top`
 //                largest c are chosen (ties: the lower index); the weights are the chosen experts' s, as they are.
 //                Options: s = sigmoid(logit) per expert instead of the softmax; no correction; `extra` further rows behind the
 //                experts' rows of the router matrix whose float32 logits are handed out as they are (a gate that reads the
@@ -44,7 +44,8 @@ __device__ __forceinline__ void warp_best(float& bv, int& bi) {
 
 // One warp makes one token's choice from its logits s[E] (left as softmax scores); c and gb are scratch of E floats each.
 __device__ __forceinline__ void warp_choose(float* s, float* c, float* gb, const float* __restrict__ corr, int E, int top, int g_count,
-                                            int g_keep, int* __restrict__ chosen, float* __restrict__ weights, int lane, int sigmoid_scores) {
+                                            int g_keep, int* __restrict__ chosen, float* __restrict__ weights, int lane, int sigmoid_scores,
+                                            int group_top2, int renorm, float weight_eps, float route_scale) {
     if (sigmoid_scores) {
         for (int e = lane; e < E; e += 32) { s[e] = 1.f / (1.f + expf(-s[e])); c[e] = corr ? s[e] + corr[e] : s[e]; }
     } else {
@@ -59,9 +60,12 @@ __device__ __forceinline__ void warp_choose(float* s, float* c, float* gb, const
     if (g_count > 0) {
         const int per = E / g_count;
         for (int g = lane; g < g_count; g += 32) {
-            float b = -INFINITY;
-            for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, c[e]);
-            gb[g] = b;
+            float b = -INFINITY, b2 = -INFINITY;               // the largest and the second largest choice score of the group
+            for (int e = g * per; e < (g + 1) * per; ++e) {
+                const float v = c[e];
+                if (v > b) { b2 = b; b = v; } else if (v > b2) b2 = v;
+            }
+            gb[g] = group_top2 && per > 1 ? b + b2 : b;
         }
         __syncwarp();
         for (int k = 0; k < g_keep; ++k) {                 // a kept group's entry becomes +inf
@@ -89,6 +93,14 @@ __device__ __forceinline__ void warp_choose(float* s, float* c, float* gb, const
         if (lane == 0) { chosen[j] = bi; weights[j] = s[bi]; c[bi] = NAN; }       // NaN: taken
         __syncwarp();
     }
+    if (renorm || route_scale != 1.f) {                     // weights <- weights / (their sum + eps) * route_scale, summed in the order of choice
+        if (lane == 0) {
+            float sum = 0.f;
+            for (int j = 0; j < top; ++j) sum += weights[j];
+            for (int j = 0; j < top; ++j) weights[j] = renorm ? weights[j] / (sum + weight_eps) * route_scale : weights[j] * route_scale;
+        }
+        __syncwarp();
+    }
 }
 
 // One block per TOK tokens: 8 warps for 8 tokens (prompt steps), up to a warp per expert for one token (decode steps, where the
@@ -99,7 +111,8 @@ __device__ __forceinline__ void warp_choose(float* s, float* c, float* gb, const
 template <typename T, int TOK>
 __global__ void __launch_bounds__(TOK == 1 ? 1024 : 256) route_topk_kernel(const T* __restrict__ h, int ldh, const T* __restrict__ router, const float* __restrict__ corr,
                                                          int* __restrict__ chosen, float* __restrict__ weights, int T_, int hidden, int E, int top,
-                                                         int g_count, int g_keep, int sigmoid_scores, int extra, float* __restrict__ extra_out) {
+                                                         int g_count, int g_keep, int sigmoid_scores, int extra, float* __restrict__ extra_out,
+                                                         int group_top2, int renorm, float weight_eps, float route_scale) {
     extern __shared__ __align__(16) float rsm[];
     const int EA = E + extra;                          // rows of the router matrix: the experts', then the extra ones
     float* hs = rsm;                                   // [TOK][hidden]
@@ -148,7 +161,8 @@ __global__ void __launch_bounds__(TOK == 1 ? 1024 : 256) route_topk_kernel(const
         float* s = sc + (size_t)tk * 3 * EA;
         const size_t t = t0 + tk;
         for (int r = lane; r < extra; r += 32) extra_out[t * extra + r] = s[E + r];
-        warp_choose(s, s + EA, s + 2 * EA, corr, E, top, g_count, g_keep, chosen + t * top, weights + t * top, lane, sigmoid_scores);
+        warp_choose(s, s + EA, s + 2 * EA, corr, E, top, g_count, g_keep, chosen + t * top, weights + t * top, lane, sigmoid_scores,
+                    group_top2, renorm, weight_eps, route_scale);
     }
 }
 
@@ -434,9 +448,11 @@ MI_EXPORT int mi_moe_scale_rows(const void* h, int ldh, const float* weights, in
 }
 
 // router [E + extra, hidden] in the dtype of h (its values are read as they are stored and multiplied and added in float32)
+// group_top2: a group is ranked by the sum of its two largest choice scores (0: by its largest); renorm: the chosen scores are divided
+// by their sum + weight_eps; route_scale multiplies the weights last
 MI_EXPORT int mi_route_topk(const void* h, int ldh, const void* router, const float* corr, int* chosen, float* weights, int T_, int hidden,
-                            int E, int top, int g_count, int g_keep, int sigmoid_scores, int extra, float* extra_out, int dtype,
-                            cudaStream_t stream) {
+                            int E, int top, int g_count, int g_keep, int sigmoid_scores, int extra, float* extra_out, int group_top2,
+                            int renorm, float weight_eps, float route_scale, int dtype, cudaStream_t stream) {
     if (T_ == 0) return 0;
     if (top > E || (g_count > 0 && E % g_count) || extra < 0 || (extra > 0 && !extra_out)) return -2;
     const int tok = T_ >= 1024 ? 8 : 1;
@@ -446,7 +462,7 @@ MI_EXPORT int mi_route_topk(const void* h, int ldh, const void* router, const fl
 #define GO(T, TOK) do { \
         if (smem > 48 * 1024) cudaFuncSetAttribute(route_topk_kernel<T, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         route_topk_kernel<T, TOK><<<grid, TOK == 1 ? min(1024, max(128, 32 * (E + extra))) : 256, smem, stream>>>((const T*)h, ldh, (const T*)router, corr, chosen, weights, T_, hidden, E, top, \
-                                                               g_count, g_keep, sigmoid_scores, extra, extra_out); } while (0)
+                                                               g_count, g_keep, sigmoid_scores, extra, extra_out, group_top2, renorm, weight_eps, route_scale); } while (0)
     if (dtype == MI_BF16) { if (tok == 8) GO(__nv_bfloat16, 8); else GO(__nv_bfloat16, 1); }
     else { if (tok == 8) GO(float, 8); else GO(float, 1); }
 #undef GO

@@ -107,7 +107,7 @@ template <typename T>
 __global__ void head_gate_kernel(const T* __restrict__ o, const T* __restrict__ gate, int gate_stride, T* __restrict__ y, int T_, int H, int V) {
     const size_t t = blockIdx.x;
     const int h = blockIdx.y;
-    const float sg = 1.f / (1.f + expf(-to_f32(gate[t * gate_stride + h])));
+    const float sg = gate ? 1.f / (1.f + expf(-to_f32(gate[t * gate_stride + h]))) : 1.f;      // no gate: the heads are only laid side by side
     const T* src = o + ((size_t)h * T_ + t) * V;
     T* dst = y + (t * H + h) * V;
     for (int i = threadIdx.x; i < V; i += blockDim.x) dst[i] = from_f32<T>(to_f32(src[i]) * sg);

@@ -1,2 +1,2 @@
 """Built-in architectures; importing this package registers them."""
-from . import naditar, namesun, nununex, qwen3  # noqa: F401
+from . import megovik, naditar, namesun, nununex, qwen3  # noqa: F401

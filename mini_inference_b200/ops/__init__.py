@@ -652,11 +652,12 @@ class CudaOps:
         return y
 
     def head_gate(self, o, gate, out_dtype):
-        """o [H, T, V], gate [T, H] (a strided view is allowed) -> rows [T, H V] = o * sigmoid(gate) per head."""
+        """o [H, T, V], gate [T, H] (a strided view is allowed) -> rows [T, H V] = o * sigmoid(gate) per head; gate None: the
+        heads laid side by side as they are."""
         H, T, V = o.shape
-        assert o.is_contiguous() and gate.stride(1) == 1 and o.dtype == out_dtype == gate.dtype
+        assert o.is_contiguous() and o.dtype == out_dtype and (gate is None or (gate.stride(1) == 1 and gate.dtype == out_dtype))
         y = torch.empty((T, H * V), dtype=out_dtype, device=o.device)
-        _check(self.lib.mi_head_gate(_p(o), _p(gate), gate.stride(0), _p(y), T, H, V, _code(out_dtype), self._stream()), "head_gate")
+        _check(self.lib.mi_head_gate(_p(o), _p(gate), 0 if gate is None else gate.stride(0), _p(y), T, H, V, _code(out_dtype), self._stream()), "head_gate")
         self.launches += 1
         return y
 
@@ -720,14 +721,16 @@ class CudaOps:
         self.launches += H
         return out
 
-    def latent_prepare(self, p, q_abs, H, D, R, C, norm_w, eps, inv_freq, meta, cache):
+    def latent_prepare(self, p, q_abs, H, D, R, C, norm_w, eps, inv_freq, meta, cache, q_rows=None, dkv_col=None):
         """p [T, ..] = q heads [H, D + R] | dkv [C + R] | ..; q_abs [H, T, C].  Returns q [T, H, C + R] = [q_abs | rotated
-        q part]; writes the token's cache row [rmsnorm(dkv[:C]) * norm_w | rotated dkv[C:]] at its slot (cache None: no write)."""
+        q part]; writes the token's cache row [rmsnorm(dkv[:C]) * norm_w | rotated dkv[C:]] at its slot (cache None: no write).
+        q_rows [T, H (D + R)]: the query heads lie in a tensor of their own; dkv_col: the column of p at which dkv starts."""
         T = p.shape[0]
-        assert p.stride(1) == 1 and q_abs.is_contiguous()
+        assert p.stride(1) == 1 and q_abs.is_contiguous() and (q_rows is None or (q_rows.stride(1) == 1 and q_rows.dtype == p.dtype))
         q = torch.empty((T, H, C + R), dtype=p.dtype, device=p.device)
         nf = 0 if inv_freq is None else inv_freq.numel()
-        _check(self.lib.mi_latent_prepare(_p(p), p.stride(0), _p(q_abs), _p(q), _p(cache), _p(norm_w), _p(inv_freq), nf,
+        _check(self.lib.mi_latent_prepare(_p(p), p.stride(0), _p(q_rows), 0 if q_rows is None else q_rows.stride(0),
+                                          -1 if dkv_col is None else int(dkv_col), _p(q_abs), _p(q), _p(cache), _p(norm_w), _p(inv_freq), nf,
                                           _p(meta.positions), _p(meta.slots), T, H, D, R, C, _c.c_float(eps), _code(p.dtype),
                                           self._stream()), "latent_prepare")
         self.launches += 1
@@ -824,34 +827,43 @@ class CudaOps:
         return y
 
     # ---------------------------------------------------------------- attention with a block mask, a sink and unit-norm q, k
-    def unit_qk_cache(self, p, H, KV, D, V, eps, lam, source, meta, k_cache, v_cache):
+    def unit_qk_cache(self, p, H, KV, D, V, eps, lam, source, meta, k_cache, v_cache, q_weight=None, k_weight=None, q_temp=None,
+                      values_are_keys=False):
         """p [T, H D + KV D + KV V] = q | k | v.  q and k are divided by their root mean square per head (eps None: left as they
         are), q in place; v becomes (1 - lam) v + lam source when source [T, KV V] (another layer's values, a view is allowed) is
-        given; k and v go to the rows' slots of the caches (None: this layer writes none).  Returns the q view."""
+        given; k and v go to the rows' slots of the caches (None: this layer writes none).  Returns the q view.
+        q_weight, k_weight float32 [D]: multiplied in after the division (shared by all heads); q_temp (coef, every): q at position p
+        is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1); values_are_keys: p has no v columns and the cached values are
+        the keys as projected, before the norm."""
         T = p.shape[0]
-        assert p.is_contiguous() and p.shape[1] == (H + KV) * D + KV * V
+        assert p.is_contiguous() and p.shape[1] == (H + KV) * D + (0 if values_are_keys else KV * V)
         assert source is None or (source.stride(1) == 1 and source.dtype == p.dtype and lam is not None)
-        _check(self.lib.mi_unit_qk_cache(_p(p), p.stride(0), _p(source), 0 if source is None else source.stride(0), _p(lam if source is not None else None),
-                                         _p(meta.slots), _p(k_cache), _p(v_cache), T, H, KV, D, V, meta.page_size,
-                                         _c.c_float(eps or 0.0), int(eps is not None), _code(p.dtype), self._stream()), "unit_qk_cache")
+        assert q_weight is None or (q_weight.dtype == k_weight.dtype == torch.float32 and q_weight.numel() == k_weight.numel() == D)
+        coef, every = q_temp if q_temp else (0.0, 0)
+        _check(self.lib.mi_normed_qk_cache(_p(p), p.stride(0), _p(source), 0 if source is None else source.stride(0), _p(lam if source is not None else None),
+                                           _p(meta.slots), _p(k_cache), _p(v_cache), T, H, KV, D, V, meta.page_size,
+                                           _c.c_float(eps or 0.0), int(eps is not None), _p(q_weight), _p(k_weight), _p(meta.positions),
+                                           _c.c_float(coef), int(every), int(bool(values_are_keys)), _code(p.dtype), self._stream()), "unit_qk_cache")
         self.launches += 1
         return p[:, :H * D]
 
     def masked_attention(self, q, k_cache, v_cache, meta, H, KV, D, V, scale, block_size, window, sink, sink_values=None, distance_bias=None,
-                         distance_bias_by_head=None):
+                         distance_bias_by_head=None, distance_slopes=None):
         """q [T, H D] (a strided view is allowed) over the pages; keys of D and values of V entries; block_size / window / sink as
         csrc/attention_masked.cu states them.  sink_values float32 [H]: the sink's score per head (None: 0); distance_bias float32
         [far + 1, H]: added to the scaled score by the distance i - j (beyond far: the last row); distance_bias_by_head: the same
-        table as float32 [H, far + 1], for the kernels that read it along the distance.  Scores, weights and sums are float32.
-        Returns [T, H V]."""
+        table as float32 [H, far + 1], for the kernels that read it along the distance.  distance_slopes float32 [H]: slope_h * (i - j)
+        is taken off the scaled score of head h.  Scores, weights and sums are float32.  Returns [T, H V]."""
         T = q.shape[0]
         assert q.stride(1) == 1
         out = torch.empty((T, H * V), dtype=q.dtype, device=q.device)
         code, blk, win = _code(q.dtype), int(block_size or 0), int(window or 0)
         rows = getattr(meta, "table_rows", None)
         num_decode, num_tiles = meta.decode_segs.shape[0], meta.prefill_tiles.shape[0]
-        plain = sink_values is None and distance_bias is None
+        slopes = distance_slopes
+        plain = sink_values is None and distance_bias is None and slopes is None
         if not plain:
+            assert slopes is None or (slopes.dtype == torch.float32 and slopes.is_contiguous() and slopes.numel() == H)
             assert sink_values is None or (sink and sink_values.dtype == torch.float32 and sink_values.numel() == H)
             assert distance_bias is None or (distance_bias.dtype == torch.float32 and distance_bias.is_contiguous() and distance_bias.shape[1] == H)
         bias_last = 0 if distance_bias is None else distance_bias.shape[0] - 1
@@ -864,7 +876,7 @@ class CudaOps:
                 _p(meta.seg_pos0), _p(meta.block_table), _p(rows), meta.max_pages, H, KV, D, meta.page_size, meta.tile,
                 _c.c_float(scale), win, blk, int(bool(sink)), self._stream()), "attn_prefill_mma_masked")
             self.launches += 1
-        elif (num_tiles and self.fast_attention and self.biased_attention_tc and q.dtype == torch.bfloat16 and D == V and D in (64, 128)
+        elif (num_tiles and slopes is None and self.fast_attention and self.biased_attention_tc and q.dtype == torch.bfloat16 and D == V and D in (64, 128)
                 and meta.tile == 64 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
             # the same kernel with the learned sink's score and the distance table (one row per head) in its softmax
             bias_t = self._bias_rows_by_head(distance_bias, distance_bias_by_head, H, q.device)
@@ -877,13 +889,13 @@ class CudaOps:
             _check(self.lib.mi_masked_prefill(
                 _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(meta.prefill_tiles), num_tiles, _p(meta.seg_q_start),
                 _p(meta.seg_pos0), _p(meta.block_table), _p(rows), meta.max_pages, H, KV, D, V, meta.page_size, meta.tile,
-                _c.c_float(scale), blk, win, int(bool(sink)), _p(sink_values), _p(distance_bias), bias_last, code, self._stream()), "masked_prefill")
+                _c.c_float(scale), blk, win, int(bool(sink)), _p(sink_values), _p(distance_bias), bias_last, _p(slopes), code, self._stream()), "masked_prefill")
             self.launches += 1
         if not num_decode:
             return out
         reach = meta.max_kv_len if not blk else min(meta.max_kv_len, blk)              # the most keys a decoded token can see
         reach = reach if not win else min(reach, win)
-        if ((plain or self.biased_attention_tc) and self.fast_attention and q.dtype == torch.bfloat16 and D == V and D in (64, 128) and H // KV <= 16
+        if ((plain or self.biased_attention_tc) and slopes is None and self.fast_attention and q.dtype == torch.bfloat16 and D == V and D in (64, 128) and H // KV <= 16
                 and meta.page_size % 16 == 0 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
             # the tensor-core decode kernel (the G query heads of a kv head are the rows of one tile), split weights
             S = self.choose_splits(num_decode * KV, reach, 2 if self.bulk_decode else 3, cluster=self.bulk_decode and self.cluster_merge, head_dim=D)
@@ -921,7 +933,7 @@ class CudaOps:
             _check(self.lib.mi_masked_decode(
                 _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(o_part), _p(lse), _p(meta.decode_segs), num_decode,
                 _p(meta.seg_q_start), _p(meta.seg_kv_len), _p(meta.block_table), _p(rows), meta.max_pages, H, KV, D, V,
-                meta.page_size, S, _c.c_float(scale), blk, win, int(bool(sink)), _p(sink_values), _p(distance_bias), bias_last, code,
+                meta.page_size, S, _c.c_float(scale), blk, win, int(bool(sink)), _p(sink_values), _p(distance_bias), bias_last, _p(slopes), code,
                 self._stream()), "masked_decode")
             self.launches += 2 if S > 1 else 1
         return out
@@ -957,11 +969,14 @@ class CudaOps:
         return out
 
     # ---------------------------------------------------------------- routed experts
-    def route_topk(self, h, router, correction, top, groups, score=None, extra_rows=0):
+    def route_topk(self, h, router, correction, top, groups, score=None, extra_rows=0, group_score="max", renormalise=False, weight_eps=0.0,
+                   route_scale=1.0):
         """(chosen int32 [T, top], weights float32 [T, top]).  router [E, hidden] in the dtype of h, correction float32 [E] or None;
         groups None or (count, keep).  Products, sums, scores and the choice are float32 (csrc/moe.cu).  Called with `score`
         ("softmax" or "sigmoid") it answers (chosen, weights, extra): the router matrix then has extra_rows more rows behind the
-        experts' and extra float32 [T, extra_rows] holds their logits (None without extra rows)."""
+        experts' and extra float32 [T, extra_rows] holds their logits (None without extra rows).  group_score "top2_sum": a group is
+        ranked by the sum of its two largest choice scores; renormalise: the weights are divided by their sum + weight_eps; route_scale
+        multiplies them last."""
         T, E = h.shape[0], router.shape[0] - extra_rows
         assert h.stride(1) == 1 and router.dtype == h.dtype and router.is_contiguous() and (correction is None or correction.dtype == torch.float32)
         chosen = torch.empty((T, top), dtype=torch.int32, device=h.device)
@@ -969,7 +984,9 @@ class CudaOps:
         extra = torch.empty((T, extra_rows), dtype=torch.float32, device=h.device) if extra_rows else None
         count, keep = groups if groups else (0, 0)
         _check(self.lib.mi_route_topk(_p(h), h.stride(0), _p(router), _p(correction), _p(chosen), _p(weights), T, h.shape[1], E, top,
-                                      count, keep, int(score == "sigmoid"), extra_rows, _p(extra), _code(h.dtype), self._stream()), "route_topk")
+                                      count, keep, int(score == "sigmoid"), extra_rows, _p(extra), int(group_score == "top2_sum"),
+                                      int(bool(renormalise)), _c.c_float(weight_eps), _c.c_float(route_scale), _code(h.dtype), self._stream()),
+               "route_topk")
         self.launches += 1
         return (chosen, weights) if score is None else (chosen, weights, extra)
 
@@ -1085,6 +1102,65 @@ class CudaOps:
                                     _code(z.dtype), self._stream()), "bias_act")
         self.launches += 1
         return out
+
+    def embed_scaled_stream(self, ids, table, scale, pos_table, positions):
+        """x float32 [T, hidden] = table[id] * scale + pos_table[position] (pos_table None: no positions): the start of a float32 stream."""
+        T, hidden = ids.shape[0], table.shape[1]
+        assert table.is_contiguous() and (pos_table is None or (pos_table.is_contiguous() and pos_table.dtype == table.dtype and pos_table.shape[1] == hidden))
+        x = torch.empty((T, hidden), dtype=torch.float32, device=table.device)
+        _check(self.lib.mi_embed_scaled_stream(_p(ids), _p(table), _c.c_float(scale), _p(pos_table), _p(positions), _p(x), T, hidden, table.shape[0],
+                                               0 if pos_table is None else pos_table.shape[0], _code(table.dtype), self._stream()), "embed_scaled_stream")
+        self.launches += 1
+        return x
+
+    def stream_rmsnorm_pair(self, x, a, b, bias, pre_add, weight, eps, rows, out_dtype):
+        """x (float32 stream) += a + b + bias + pre_add, each of which may be None: a, b [T, hidden] outputs of two sublayers (one
+        dtype), bias float32 [hidden], pre_add float32 [hidden] or [T, hidden]; y = weight * x / rms(x) in out_dtype.  rows: only these
+        rows are normed and the stream is left as it is.  All sums are float32, in one kernel."""
+        hidden = x.shape[-1]
+        n = x.shape[0] if rows is None else rows.shape[0]
+        y = torch.empty((n, hidden), dtype=out_dtype, device=x.device)
+        assert x.dtype == torch.float32 and x.is_contiguous()
+        for d in (a, b):
+            assert d is None or (d.is_contiguous() and d.shape == x.shape)
+        assert a is None or b is None or a.dtype == b.dtype
+        assert bias is None or (bias.dtype == torch.float32 and bias.numel() == hidden)
+        stride = 0
+        if pre_add is not None:
+            assert pre_add.dtype == torch.float32 and pre_add.is_contiguous() and pre_add.numel() in (hidden, x.numel())
+            stride = hidden if pre_add.dim() == 2 else 0
+        first = a if a is not None else b
+        _check(self.lib.mi_stream_rmsnorm_pair(_p(x), _p(a), _p(b), _p(bias), _p(pre_add), _c.c_longlong(stride), _p(weight), _p(y), _p(rows), n, hidden,
+                                               _c.c_float(eps), _code(first.dtype if first is not None else out_dtype), _code(out_dtype), self._stream()),
+               "stream_rmsnorm_pair")
+        self.launches += 1
+        return y
+
+    def rows_rmsnorm(self, x, weight, eps):
+        """y = weight * x / rms(x) over the rows of x [T, n] (a strided view is allowed); y contiguous, in x's dtype; float32 statistics."""
+        assert x.stride(1) == 1 and weight.dtype == torch.float32 and weight.numel() == x.shape[1]
+        y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        _check(self.lib.mi_rows_rmsnorm(_p(x), _c.c_longlong(x.stride(0)), _p(weight), _p(y), x.shape[0], x.shape[1], _c.c_float(eps), _code(x.dtype),
+                                        self._stream()), "rows_rmsnorm")
+        self.launches += 1
+        return y
+
+    def bias_glu(self, gu, bias, act):
+        """[g | u] (+ bias float32 [2 I], or None) -> act(g) * u, act one of relu, silu, gelu_tanh; float32 arithmetic."""
+        rows, inter = gu.shape[0], gu.shape[1] // 2
+        assert gu.is_contiguous() and (bias is None or (bias.dtype == torch.float32 and bias.numel() == 2 * inter))
+        out = torch.empty((rows, inter), dtype=gu.dtype, device=gu.device)
+        _check(self.lib.mi_bias_glu(_p(gu), _p(bias), _p(out), rows, inter, {"relu": 0, "silu": 1, "gelu_tanh": 2}[act], _code(gu.dtype),
+                                    self._stream()), "bias_glu")
+        self.launches += 1
+        return out
+
+    def scale_logits(self, logits, s):
+        """logits <- logits * s, in place (float32)."""
+        assert logits.dtype == torch.float32 and logits.is_contiguous()
+        _check(self.lib.mi_scale_f32(_p(logits), _c.c_longlong(logits.numel()), _c.c_float(s), self._stream()), "scale_logits")
+        self.launches += 1
+        return logits
 
     def softcap(self, logits, cap):
         """logits <- cap * tanh(logits / cap), in place (float32)."""

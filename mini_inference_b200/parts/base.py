@@ -62,6 +62,10 @@ a block reads the attributes, it never probes with hasattr:
                                accepts pre_add=<float32 [hidden]> (a vector added to every row of the stream before the norm);
                                embed(ids, table, ctx, float32) gathers and norms embedded tokens into a new stream.  A spec
                                with residual="float32" needs it of all its norms
+  takes_pair_delta = True  Norm: forward accepts a PairDelta as `delta` (two sublayers' outputs and a bias vector, added to the
+                               stream in float32 inside the norm's kernel) and pre_add=<float32 [T, hidden]> (added row by row)
+  absolute_table           Position: a learned [rows, hidden] table; the kernel that starts a float32 stream adds row p to the token
+                               at position p (on_embedding then has nothing left to do)
   takes_next_weight = True Norm: forward accepts next_weight=<tensor> and passes it to ctx.ops.add_rmsnorm: the block
                                names the first weight of the part that follows, and the kernel may request it into L2
 """
@@ -125,6 +129,16 @@ class GatedDelta:
         self.y, self.logits, self.bias, self.y_bias = y, logits, bias, y_bias
 
 
+class PairDelta:
+    """An addition to the residual stream made of two sublayers' outputs that read the same normed rows: the stream receives
+    a + b (+ bias, a float32 vector added to every row; None: none), summed in float32.  b may be None (a layer with one
+    sublayer).  Only norms that declare takes_pair_delta understand it; a block hands it to the next norm, whose kernel adds it."""
+    __slots__ = ("a", "b", "bias")
+
+    def __init__(self, a, b=None, bias=None):
+        self.a, self.b, self.bias = a, b, bias
+
+
 class LayerCache:
     """What one execution step's mixer gets from the cache manager: for pages, the step's key
     and value pools [pages, kv_heads, page_size, head_dim] and the index of the cache group
@@ -171,6 +185,9 @@ class Part:
     takes_next_weight = False
     keeps_float32_stream = False     # Norm: reads and writes a float32 residual stream whatever the run's dtype, takes pre_add=
     takes_gated_delta = False        # Norm: `delta` may be a GatedDelta, applied to the stream in the norm's kernel
+    takes_pair_delta = False         # Norm: `delta` may be a PairDelta; pre_add may be a [T, hidden] float32 tensor added row by row
+    adds_to_embedding = False        # Position: owns an absolute_table (known before the weights are loaded)
+    absolute_table = None            # Position: a [rows, hidden] table whose row p the embedding kernel adds to the token at position p
     owns_state = False               # Block: cache_need() gives the step's whole need (its own parts' state beside the mixer's)
     offers_unbiased = False          # FeedForward: forward_unbiased(h, ctx) -> (y, bias): forward == y + bias, the addition left to the caller
     step_arrays_key: Optional[str] = None

@@ -9,7 +9,7 @@ with defer=True when every norm of the model accepts deferred sums; a norm that 
 told which weight the following part streams first."""
 from __future__ import annotations
 
-from .base import GatedDelta, Part, StateNeed, flatten_needs, register_block
+from .base import GatedDelta, PairDelta, Part, StateNeed, flatten_needs, register_block
 
 
 @register_block("prenorm")
@@ -155,3 +155,39 @@ class GatedPreNormBlock(Part):
 class GatedPreNormMixerOnly(GatedPreNormBlock):
     """A layer without feed-forward: x <- x + gate1(n) * mixer(filter1(n))."""
     roles = {"mixer": "mixer", "norm1": "norm", "position": "position", "filter1": "input_filter", "gate1": "residual_gate"}
+
+
+@register_block("parallel_prenorm")
+class ParallelPreNormBlock(Part):
+    """ONE norm whose rows both sublayers read; their sum joins the stream:  n = norm1(x);  x <- x + (mixer(n) + feed_forward(n)).
+    The two outputs travel as a PairDelta to the next norm, whose kernel adds them (and the feed-forward's last bias, when the
+    feed-forward leaves it to the adder) to the stream in float32.  pre_add: what is added to the stream before this layer
+    (a vector, or a tensor row by row), in the same kernel as the pending addition."""
+    roles = {"mixer": "mixer", "feed_forward": "feed_forward", "norm1": "norm", "position": "position"}
+
+    def __init__(self, spec, parts):
+        super().__init__(spec)
+        self.parts = dict(parts)
+        self.mixer, self.feed_forward = parts["mixer"], parts.get("feed_forward")
+        self.norm1, self.position = parts["norm1"], parts["position"]
+        if not self.norm1.takes_pair_delta:
+            raise ValueError("the parallel arrangement needs a norm that adds a pair of outputs (takes_pair_delta)")
+
+    def norms(self):
+        return [self.norm1]
+
+    def forward(self, x, delta, ctx, cache, owns_cache=True, pre_add=None):
+        n = self.norm1.forward(x, delta, ctx, pre_add=pre_add)
+        a = self.mixer.forward(n, ctx, cache, self.position, owns_cache)
+        if self.feed_forward is None:
+            return x, PairDelta(a)
+        if self.feed_forward.offers_unbiased:
+            f, bias = self.feed_forward.forward_unbiased(n, ctx)
+            return x, PairDelta(a, f, bias)
+        return x, PairDelta(a, self.feed_forward.forward(n, ctx))
+
+
+@register_block("parallel_prenorm_mixer")
+class ParallelPreNormMixerOnly(ParallelPreNormBlock):
+    """A layer without feed-forward: x <- x + mixer(norm1(x)), in the same float32 arithmetic."""
+    roles = {"mixer": "mixer", "norm1": "norm", "position": "position"}

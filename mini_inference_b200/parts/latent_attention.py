@@ -10,6 +10,10 @@ absorbed into the query and the output:  q_u . (W_uk_h c) = (W_uk_h^T q_u) . c  
 sum_j p_j W_uv_h c_j = W_uv_h (sum_j p_j c_j),  so attention runs as H query heads of size
 kv_rank + rot_dim over ONE shared key row per token whose first kv_rank entries are also the value,
 for prompt portions and decoded tokens alike; neither keys nor values of a head are ever materialised.
+
+Options: rot_dim=0 (no rotated part: the cached row is the latent alone and positions do not enter); gate=False (no
+per-head output gate, no tensor `g`); q_rank=n (the queries pass a latent of their own: c_q = rmsnorm(W_dq h) * w with the
+tensor `dq.norm`, q = W_uq c_q; tensors `dq`, `dq.norm`, `uq` instead of `q`).
 """
 from __future__ import annotations
 
@@ -30,20 +34,32 @@ class LatentAttention(Part):
         self.hidden, self.H = int(g("hidden_size")), int(g("num_heads"))
         self.D, self.R, self.V, self.C = int(g("nope_dim")), int(g("rot_dim")), int(g("value_dim")), int(g("kv_rank"))
         self.scale, self.eps = float(g("scale")), float(g("latent_norm_eps"))
-        self.proj = self.uk_t = self.uv = self.o = self.latent_norm = None
+        self.gate = bool(g("gate", True))
+        self.q_rank = int(g("q_rank")) if g("q_rank") else None
+        self.proj = self.uk_t = self.uv = self.o = self.latent_norm = self.uq = self.q_norm = None
 
     def weight_specs(self):
         H, D, R, V, C, hid = self.H, self.D, self.R, self.V, self.C, self.hidden
-        return [WeightSpec("q", (H * (D + R), hid)), WeightSpec("dkv", (C + R, hid)),
-                WeightSpec("dkv.norm", (C,), kind="vector", init="norm"), WeightSpec("uk", (H * D, C)),
-                WeightSpec("uv", (H * V, C)), WeightSpec("g", (H, hid)), WeightSpec("o", (hid, H * V))]
+        if self.q_rank:
+            specs = [WeightSpec("dq", (self.q_rank, hid)), WeightSpec("dq.norm", (self.q_rank,), kind="vector", init="norm"),
+                     WeightSpec("uq", (H * (D + R), self.q_rank))]
+        else:
+            specs = [WeightSpec("q", (H * (D + R), hid))]
+        specs += [WeightSpec("dkv", (C + R, hid)), WeightSpec("dkv.norm", (C,), kind="vector", init="norm"),
+                  WeightSpec("uk", (H * D, C)), WeightSpec("uv", (H * V, C)), WeightSpec("o", (hid, H * V))]
+        if self.gate:
+            specs.append(WeightSpec("g", (H, hid)))
+        return specs
 
     def cache_need(self):
         return KVCacheNeed(1, self.C + self.R, None, planes=1)
 
     def load(self, tensors, dtype, device):
         H, D, V, C = self.H, self.D, self.V, self.C
-        self.proj = torch.cat([tensors.pop("q"), tensors.pop("dkv"), tensors.pop("g")], dim=0).contiguous()   # q | c, kr | gate
+        first = [tensors.pop("dq")] if self.q_rank else [tensors.pop("q")]                                     # q (or its latent) | c, kr | gate
+        self.proj = torch.cat(first + [tensors.pop("dkv")] + ([tensors.pop("g")] if self.gate else []), dim=0).contiguous()
+        if self.q_rank:
+            self.uq, self.q_norm = tensors.pop("uq"), tensors.pop("dq.norm").float().contiguous()
         self.uk_t = tensors.pop("uk").view(H, D, C).transpose(1, 2).contiguous()       # [H, C, D]: q_abs_h = uk_t_h q_u
         self.uv = tensors.pop("uv").view(H, V, C).contiguous()                         # [H, V, C]: o_h = uv_h o_lat_h
         self.latent_norm = tensors.pop("dkv.norm").float().contiguous()
@@ -71,10 +87,18 @@ class LatentAttention(Part):
         ops, H, D, R, V, C = ctx.ops, self.H, self.D, self.R, self.V, self.C
         meta = ctx.batch.group_view(cache.group, self.step_arrays_key)
         p = ops.linear(h, self.proj)                                               # [T, H (D + R) + C + R + H]
-        q_abs = ops.batched_linear(p, 0, D + R, D, self.uk_t)                      # [H, T, C]
-        q = ops.latent_prepare(p, q_abs, H, D, R, C, self.latent_norm, self.eps, position.rotary_inv_freq(), meta,
-                               cache.k if owns_cache else None)                    # [T, H, C + R]; [c | kr] -> the pages
+        if self.q_rank:                                                            # p = c_q as projected | c, kr | gate
+            qp = ops.linear(ops.rows_rmsnorm(p[:, :self.q_rank], self.q_norm, self.eps), self.uq)
+            q_abs = ops.batched_linear(qp, 0, D + R, D, self.uk_t)
+            q = ops.latent_prepare(p, q_abs, H, D, R, C, self.latent_norm, self.eps, position.rotary_inv_freq(), meta,
+                                   cache.k if owns_cache else None, q_rows=qp, dkv_col=self.q_rank)
+            gate_col = self.q_rank + C + R
+        else:
+            q_abs = ops.batched_linear(p, 0, D + R, D, self.uk_t)                  # [H, T, C]
+            q = ops.latent_prepare(p, q_abs, H, D, R, C, self.latent_norm, self.eps, position.rotary_inv_freq(), meta,
+                                   cache.k if owns_cache else None)                # [T, H, C + R]; [c | kr] -> the pages
+            gate_col = H * (D + R) + C + R
         o_lat = ops.latent_attention(q, cache.k, meta, H, C, R, self.scale)        # [H, T, C]
         o = ops.batched_linear(o_lat, None, None, C, self.uv)                      # [H, T, V]
-        rows = ops.head_gate(o, p[:, H * (D + R) + C + R:], ctx.dtype)             # [T, H V]
+        rows = ops.head_gate(o, p[:, gate_col:] if self.gate else None, ctx.dtype)  # [T, H V]
         return rows, self.o

@@ -97,7 +97,9 @@ class RoutedExperts(Part):
     correction tensor: the choice is made on s itself); act="silu" (an expert is W_down(silu(W_gate h) * W_up h), no clamps);
     weight_on="input" (a chosen expert's score multiplies its INPUT, out = sum expert(s * h), instead of its output);
     shared_gate=True (the shared expert's output is multiplied by sigmoid(w_sg . h), one number per token, tensor `shared.sg`;
-    its logit is made in float32 beside the router's)."""
+    its logit is made in float32 beside the router's); group_score="top2_sum" (a group is ranked by the sum of its two largest
+    choice scores instead of its largest; a group of one expert by that expert's); renormalise=True (the chosen experts' scores are
+    divided by their sum + weight_eps); route_scale (the weights are multiplied by it, after the division if there is one)."""
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -108,6 +110,11 @@ class RoutedExperts(Part):
         if self.score not in ("softmax", "sigmoid") or self.act not in ("clamped", "silu") or self.weight_on not in ("output", "input"):
             raise ValueError("routed_experts: score is softmax or sigmoid, act clamped or silu, weight_on output or input")
         self.has_correction, self.shared_gate = bool(g("correction", True)), bool(g("shared_gate", False))
+        self.group_score, self.renormalise = g("group_score", "max"), bool(g("renormalise", False))
+        self.weight_eps, self.route_scale = float(g("weight_eps", 0.0)), float(g("route_scale", 1.0))
+        if self.group_score not in ("max", "top2_sum"):
+            raise ValueError("routed_experts: group_score is max or top2_sum")
+        self.plain_weights = self.group_score == "max" and not self.renormalise and self.route_scale == 1.0
         self.limit = float(g("limit")) if self.act == "clamped" else float("inf")
         self.slope = float(g("gate_slope", 1.702)) if self.act == "clamped" else 1.0
         self.up_shift = 1.0 if self.act == "clamped" else 0.0
@@ -152,7 +159,11 @@ class RoutedExperts(Part):
 
     def forward(self, h, ctx):
         ops = ctx.ops
-        if self.score == "softmax" and not self.shared_gate:
+        if not self.plain_weights:
+            chosen, weights, extra = ops.route_topk(h, self.router, self.correction, self.top, self.groups, score=self.score,
+                                                    extra_rows=int(self.shared_gate), group_score=self.group_score,
+                                                    renormalise=self.renormalise, weight_eps=self.weight_eps, route_scale=self.route_scale)
+        elif self.score == "softmax" and not self.shared_gate:
             chosen, weights = ops.route_topk(h, self.router, self.correction, self.top, self.groups)
             extra = None
         else:
@@ -199,3 +210,47 @@ class SquaredReluMLP(Part):
     def forward(self, h, ctx):
         y, b = self.forward_unbiased(h, ctx)
         return ctx.ops.bias_act(y, b, "none")
+
+
+@register_feed_forward("gated_mlp")
+class GatedMLP(Part):
+    """W_down (act(W_gate h + b_gate) * (W_up h + b_up)) + b_down with act one of relu, silu, gelu_tanh; biases=False: no bias
+    anywhere.  gate and up are one [2 I, hidden] product; the first biases, the activation and the product of the two halves are
+    one kernel (float32 arithmetic on the product's values); the last bias is left to whoever adds the output to the stream
+    (forward_unbiased), or added here."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden, self.inter = int(spec.get("hidden_size")), int(spec.get("intermediate_size"))
+        self.act, self.biases = spec.get("act", "silu"), bool(spec.get("biases", False))
+        if self.act not in ("relu", "silu", "gelu_tanh"):
+            raise ValueError("gated_mlp: act is relu, silu or gelu_tanh")
+        self.offers_unbiased = self.biases
+        self.gate_up = self.down = self.gate_up_b = self.down_b = None
+
+    def weight_specs(self):
+        specs = [WeightSpec("gate", (self.inter, self.hidden)), WeightSpec("up", (self.inter, self.hidden)),
+                 WeightSpec("down", (self.hidden, self.inter))]
+        if self.biases:
+            specs += [WeightSpec("gate.b", (self.inter,), kind="vector", init="zeros"), WeightSpec("up.b", (self.inter,), kind="vector", init="zeros"),
+                      WeightSpec("down.b", (self.hidden,), kind="vector", init="zeros")]
+        return specs
+
+    def load(self, tensors, dtype, device):
+        self.gate_up = torch.cat([tensors.pop("gate"), tensors.pop("up")], dim=0).contiguous()
+        self.down = tensors.pop("down")
+        if self.biases:
+            self.gate_up_b = torch.cat([tensors.pop("gate.b").float(), tensors.pop("up.b").float()]).contiguous()
+            self.down_b = tensors.pop("down.b").float().contiguous()
+
+    @property
+    def first_weight(self):
+        return self.gate_up
+
+    def forward_unbiased(self, h, ctx):
+        ops = ctx.ops
+        return ops.linear(ops.bias_glu(ops.linear(h, self.gate_up), self.gate_up_b, self.act), self.down), self.down_b
+
+    def forward(self, h, ctx):
+        y, b = self.forward_unbiased(h, ctx)
+        return y if b is None else ctx.ops.bias_act(y, b, "none")

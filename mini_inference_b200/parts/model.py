@@ -62,6 +62,12 @@ class DecoderModel:
         if spec.residual == "float32" and not all(n.keeps_float32_stream for n in norms):
             raise ValueError("the spec keeps the residual stream in float32, but one of its norms does not offer that")
         self._norms_accept_deferred = all(n.accepts_deferred for n in norms)
+        absolute = [p for p in self._positions.values() if p.adds_to_embedding]
+        self._absolute = absolute[0] if absolute else None
+        if len(absolute) > 1 or ((absolute or spec.embedding_scale != 1.0) and
+                                 (spec.residual != "float32" or spec.embedding_norm is not None or spec.embedding_part is not None)):
+            raise ValueError("a position table and an embedding scale belong to the plain start of a float32 stream, one table at most")
+        self._adds_embedding = any(step.add_embedding for step in spec.order)
         for ws in self.final_norm.weight_specs():
             self._owned.append((spec.final_norm_name, ws, self.final_norm))
         self.embedding = None
@@ -201,6 +207,9 @@ class DecoderModel:
             x = self.embedder.forward(b.token_ids, self.embedding, ctx, caches[len(self.spec.order)] if len(caches) > len(self.spec.order) else None)
         elif self.embedding_norm is not None:                  # gather and norm in one kernel; the stream starts normed
             x = self.embedding_norm.embed(b.token_ids, self.embedding, ctx, float32=self.spec.residual == "float32")
+        elif self._absolute is not None or self.spec.embedding_scale != 1.0:      # embed[token] * scale + table[position], one kernel
+            x = ops.embed_scaled_stream(b.token_ids, self.embedding, float(self.spec.embedding_scale),
+                                        None if self._absolute is None else self._absolute.absolute_table, b.positions)
         elif self.spec.residual == "float32":                  # the stream in float32 and, beside it, its rows in the run's dtype
             x, rows = ops.embed_stream(b.token_ids, self.embedding, ctx.dtype)
             ctx.note_rows(x, rows)
@@ -209,10 +218,13 @@ class DecoderModel:
         for position in self._positions.values():
             x = position.on_embedding(x, ctx)
         delta = None
+        entered = x.clone() if self._adds_embedding else None  # the stream is rewritten in place; the passes add what entered it
         for i, step in enumerate(self.spec.order):
             src = i if step.cache_from is None else step.cache_from
             block = self.blocks[step.layer]
-            if step.add_row is None:
+            if step.add_embedding:
+                x, delta = block.forward(x, delta, ctx, caches[src], step.cache_from is None, pre_add=entered)
+            elif step.add_row is None:
                 x, delta = block.forward(x, delta, ctx, caches[src], step.cache_from is None)
             else:
                 x, delta = block.forward(x, delta, ctx, caches[src], step.cache_from is None,
@@ -221,6 +233,8 @@ class DecoderModel:
             return None
         h = self.final_norm.forward(x, delta, ctx, rows=b.logit_rows)
         logits = ops.linear(h, self.lm_head, out_dtype=torch.float32)
+        if self.spec.logit_scale != 1.0:
+            logits = ops.scale_logits(logits, float(self.spec.logit_scale))
         if self.spec.logit_softcap is not None:
             logits = ops.softcap(logits, float(self.spec.logit_softcap))
         return logits

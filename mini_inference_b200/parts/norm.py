@@ -5,7 +5,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import Part, WeightSpec, register_norm
+from .base import PairDelta, Part, WeightSpec, register_norm
 
 
 @register_norm("rmsnorm")
@@ -62,6 +62,7 @@ class StreamRMSNorm(Part):
     (a pending delta, if any, is added to the stream first, in float32; a GatedDelta is gated in the same kernel)."""
     keeps_float32_stream = True
     takes_gated_delta = True
+    takes_pair_delta = True
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -75,8 +76,10 @@ class StreamRMSNorm(Part):
         self.weight = tensors["weight"].float().contiguous()
 
     def forward(self, x, delta, ctx, rows=None, pre_add=None):
-        if pre_add is not None:
-            raise ValueError("stream_rmsnorm takes no pass vector")
+        """pre_add: float32 [hidden] (a vector for every row) or [T, hidden] (row by row), added to the stream with the delta."""
+        if pre_add is not None or isinstance(delta, PairDelta):
+            pair = delta if isinstance(delta, PairDelta) else PairDelta(delta)
+            return ctx.ops.stream_rmsnorm_pair(x, pair.a, pair.b, pair.bias, pre_add, self.weight, self.eps, rows, ctx.dtype)
         return ctx.ops.stream_rmsnorm(x, delta, self.weight, self.eps, rows, ctx.dtype)
 
 

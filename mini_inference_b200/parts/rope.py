@@ -5,7 +5,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import Part, register_position
+from .base import Part, WeightSpec, register_position
 
 
 @register_position("rotary")
@@ -82,6 +82,36 @@ class HalfRotary(Part):
 
     def rotary_inv_freq(self):
         return self._inv_freq
+
+    def on_embedding(self, x, ctx):
+        return x
+
+
+@register_position("learned_absolute")
+class LearnedAbsolute(Part):
+    """A learned vector per position, added to the embedded token (after the embedding's own scale, itself unscaled):
+    x_t = embed[token_t] * scale + table[p_t].  The table is handed to the kernel that starts the float32 stream
+    (Part.absolute_table), which adds it in the same pass; mixers of such a model rotate nothing."""
+    adds_to_embedding = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.size, self.rows = int(spec.get("size")), int(spec.get("rows"))
+        self.table = None
+
+    def weight_specs(self):
+        return [WeightSpec("table", (self.rows, self.size))]
+
+    def load(self, tensors, dtype, device):
+        if "table" in tensors:
+            self.table = tensors["table"]
+
+    @property
+    def absolute_table(self):
+        return self.table
+
+    def rotary_inv_freq(self):
+        return None
 
     def on_embedding(self, x, ctx):
         return x

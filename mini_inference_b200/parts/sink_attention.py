@@ -15,6 +15,11 @@
                (one row per distance near by, logarithmic steps that reach the last row at `far`).  The table is spread out
                once, when the weights are loaded, into one float32 row per distance 0 .. far, which the kernels index directly
   key and value rows may differ in size (key_dim, value_dim); the value pool is then a tensor of its own.
+  norm_weights True: the per-head norm of q and k multiplies by a learned weight of key_dim entries that all heads share (tensors
+               `q.norm`, `k.norm`) after the division by the root mean square (needs unit_norm_eps)
+  values       "keys": there is no value projection; a key head's values are its keys AS PROJECTED, before the norm (value_dim = key_dim)
+  q_temp       (coef, every): the normed q at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1)
+  slope_exponent  e: slope_h * (i - j) is taken off the scaled score of head h = 0 .. H-1, slope_h = 2^(-e (h + 1) / H)
 
 q, k, v come from one product; one kernel norms q and k, blends v and writes k and v into the step's pages
 before attention runs, so a portion attends to itself through the cache.  Scores, softmax weights and the weighted
@@ -47,6 +52,16 @@ class SinkAttention(Part):
             raise ValueError("distance_bias needs at least two rows and a far distance beyond half of them")
         self.value_mix = g("value_mix")
         self.mix_key = g("value_mix_key", "values")
+        self.norm_weights, self.values_are_keys = bool(g("norm_weights", False)), g("values", "projected") == "keys"
+        self.q_temp = tuple(g("q_temp")) if g("q_temp") else None                               # (coef, every)
+        self.slope_exponent = float(g("slope_exponent")) if g("slope_exponent") is not None else None
+        if g("values", "projected") not in ("projected", "keys"):
+            raise ValueError("values is one of projected, keys")
+        if self.norm_weights and self.eps is None:
+            raise ValueError("norm_weights needs unit_norm_eps")
+        if self.values_are_keys and (self.V != self.D or self.value_mix):
+            raise ValueError("values that are the keys have the keys' size and are not blended")
+        self.q_norm = self.k_norm = self.slopes = None
         if self.H % self.KV:
             raise ValueError(f"{self.H} query heads are not a multiple of {self.KV} kv heads")
         if self.value_mix not in (None, "source", "blend"):
@@ -55,8 +70,11 @@ class SinkAttention(Part):
 
     def weight_specs(self):
         H, KV, D, V, hid = self.H, self.KV, self.D, self.V, self.hidden
-        specs = [WeightSpec("q", (H * D, hid)), WeightSpec("k", (KV * D, hid)), WeightSpec("v", (KV * V, hid)),
-                 WeightSpec("o", (hid, H * V))]
+        specs = [WeightSpec("q", (H * D, hid)), WeightSpec("k", (KV * D, hid)), WeightSpec("o", (hid, H * V))]
+        if not self.values_are_keys:
+            specs.append(WeightSpec("v", (KV * V, hid)))
+        if self.norm_weights:
+            specs += [WeightSpec("q.norm", (D,), kind="vector", init="norm"), WeightSpec("k.norm", (D,), kind="vector", init="norm")]
         if self.value_mix:                                  # a source layer's checkpoint holds the number too; it is not used
             specs.append(WeightSpec("vmix", (), kind="vector", init="norm"))
         if self.learned_sink:
@@ -76,8 +94,12 @@ class SinkAttention(Part):
         return KVCacheNeed(self.KV, self.D, self.window, value_dim=None if self.V == self.D else self.V)
 
     def load(self, tensors, dtype, device):
-        self.qkv = torch.cat([tensors.pop("q"), tensors.pop("k"), tensors.pop("v")], dim=0).contiguous()
+        self.qkv = torch.cat([tensors.pop("q"), tensors.pop("k")] + ([] if self.values_are_keys else [tensors.pop("v")]), dim=0).contiguous()
         self.o = tensors.pop("o")
+        if self.norm_weights:
+            self.q_norm, self.k_norm = tensors.pop("q.norm").float().contiguous(), tensors.pop("k.norm").float().contiguous()
+        if self.slope_exponent is not None:
+            self.slopes = torch.tensor([2.0 ** (-self.slope_exponent * (h + 1) / self.H) for h in range(self.H)], dtype=torch.float32, device=device)
         if self.value_mix == "blend":
             self.lam = tensors["vmix"].float().reshape(1).contiguous()
         if self.learned_sink:
@@ -110,9 +132,18 @@ class SinkAttention(Part):
                 raise ValueError("a layer that blends values in runs before the layer that lends them, or their sizes differ")
         elif self.value_mix == "source":
             ctx.shared[("value_mix", self.mix_key)] = p[:, (H + KV) * D:]      # a view: the kernel below leaves these columns alone
-        q = ops.unit_qk_cache(p, H, KV, D, V, self.eps, self.lam, source, meta,
-                              cache.k if owns_cache else None, cache.v if owns_cache else None)
-        if self.learned_sink or self.distance_bias:
+        if self.norm_weights or self.values_are_keys or self.q_temp:
+            q = ops.unit_qk_cache(p, H, KV, D, V, self.eps, self.lam, source, meta, cache.k if owns_cache else None,
+                                  cache.v if owns_cache else None, q_weight=self.q_norm, k_weight=self.k_norm, q_temp=self.q_temp,
+                                  values_are_keys=self.values_are_keys)
+        else:
+            q = ops.unit_qk_cache(p, H, KV, D, V, self.eps, self.lam, source, meta,
+                                  cache.k if owns_cache else None, cache.v if owns_cache else None)
+        if self.slopes is not None:
+            o = ops.masked_attention(q, cache.k, cache.v, meta, H, KV, D, V, self.scale, self.block_size, self.window, self.sink,
+                                     sink_values=self.sink_values, distance_bias=self.bias_by_distance,
+                                     distance_bias_by_head=self.bias_by_head, distance_slopes=self.slopes)
+        elif self.learned_sink or self.distance_bias:
             o = ops.masked_attention(q, cache.k, cache.v, meta, H, KV, D, V, self.scale, self.block_size, self.window, self.sink,
                                      sink_values=self.sink_values, distance_bias=self.bias_by_distance,
                                      distance_bias_by_head=self.bias_by_head)

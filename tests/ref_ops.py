@@ -616,7 +616,159 @@ def _softcap(self, logits, cap):
     return cap * torch.tanh(logits / cap)
 
 
+
+# ---------------------------------------------------------------- scaled embedding with positions, pair additions, row norms, gated bias activation,
+# normed q/k with a temperature and keys as values, distance slopes, group-limited sigmoid routing with renormalised weights
+def _embed_scaled_stream(self, ids, table, scale, pos_table, positions):
+    x = table[ids.long()].float() * scale
+    return x if pos_table is None else x + pos_table[positions.long()].float()
+
+
+def _stream_rmsnorm_pair(self, x, a, b, bias, pre_add, weight, eps, rows, out_dtype):
+    add = torch.zeros_like(x)
+    for part in (a, b):
+        if part is not None:
+            add = add + part.float()
+    if bias is not None:
+        add = add + bias.float()
+    if pre_add is not None:
+        add = add + pre_add.float()
+    if rows is None:
+        x.add_(add)
+        src = x
+    else:
+        src = x[rows.long()] + add[rows.long()]
+    return (_rms(src, eps) * weight.float()).to(out_dtype)
+
+
+def _rows_rmsnorm(self, x, weight, eps):
+    return (_rms(x.float(), eps) * weight.float()).to(x.dtype).contiguous()
+
+
+def _bias_glu(self, gu, bias, act):
+    y = gu.float() if bias is None else gu.float() + bias.float()
+    g, u = y.chunk(2, dim=-1)
+    f = {"relu": torch.relu, "silu": torch.nn.functional.silu, "gelu_tanh": lambda z: torch.nn.functional.gelu(z, approximate="tanh")}[act]
+    return (f(g) * u).to(gu.dtype)
+
+
+def _scale_logits(self, logits, s):
+    return logits * s
+
+
+_latent_prepare_plain = _latent_prepare
+
+
+def _latent_prepare_general(self, p, q_abs, H, D, R, C, norm_w, eps, inv_freq, meta, cache, q_rows=None, dkv_col=None):
+    if q_rows is None and dkv_col is None and R:
+        return _latent_prepare_plain(self, p, q_abs, H, D, R, C, norm_w, eps, inv_freq, meta, cache)
+    T, dt = p.shape[0], p.dtype
+    src = p if q_rows is None else q_rows
+    col = H * (D + R) if dkv_col is None else dkv_col
+    parts = [q_abs.transpose(0, 1).float()]
+    if R:
+        parts.append(_rotate_pairs(src[:, :H * (D + R)].view(T, H, D + R)[:, :, D:].float(), meta.positions, inv_freq))
+    q = torch.cat(parts, dim=-1).to(dt)
+    if cache is not None:
+        dkv = p[:, col:col + C + R].float()
+        row = _rms(dkv[:, :C], eps) * norm_w.float()
+        if R:
+            row = torch.cat([row, _rotate_pairs(dkv[:, C:], meta.positions, inv_freq)], dim=-1)
+        page, off = meta.slots.long() // meta.page_size, meta.slots.long() % meta.page_size
+        cache[page, 0, off, :] = row.to(cache.dtype)
+    return q.contiguous()
+
+
+_head_gate_plain = _head_gate
+
+
+def _head_gate_optional(self, o, gate, out_dtype):
+    if gate is not None:
+        return _head_gate_plain(self, o, gate, out_dtype)
+    H, T, V = o.shape
+    return o.transpose(0, 1).reshape(T, H * V).to(out_dtype)
+
+
+_unit_qk_cache_plain = _unit_qk_cache
+
+
+def _unit_qk_cache_general(self, p, H, KV, D, V, eps, lam, source, meta, k_cache, v_cache, q_weight=None, k_weight=None, q_temp=None,
+                           values_are_keys=False):
+    if q_weight is None and q_temp is None and not values_are_keys:
+        return _unit_qk_cache_plain(self, p, H, KV, D, V, eps, lam, source, meta, k_cache, v_cache)
+    T, dt = p.shape[0], p.dtype
+    q = p[:, :H * D].float().view(T, H, D)
+    k_raw = p[:, H * D:(H + KV) * D].float().view(T, KV, D)
+    v = k_raw if values_are_keys else p[:, (H + KV) * D:].float().view(T, KV, V)
+    k = k_raw
+    if eps is not None:
+        q, k = _rms(q, eps), _rms(k_raw, eps)
+    if q_weight is not None:
+        q, k = q * q_weight.float(), k * k_weight.float()
+    if q_temp is not None:
+        coef, every = q_temp
+        pos = meta.positions.long()
+        q = q * (1.0 + coef * torch.log(((pos + 1) // every + 1).float()))[:, None, None]
+    p[:, :H * D] = q.reshape(T, H * D).to(dt)
+    if k_cache is not None:
+        page, off = meta.slots.long() // meta.page_size, meta.slots.long() % meta.page_size
+        k_cache[page, :, off, :] = k.to(dt)
+        v_cache[page, :, off, :] = v.to(dt)
+    return p[:, :H * D]
+
+
+_masked_attention_tables = _masked_attention_biased
+
+
+def _masked_attention_sloped(self, q, k_cache, v_cache, meta, H, KV, D, V, scale, block_size, window, sink, sink_values=None,
+                             distance_bias=None, distance_bias_by_head=None, distance_slopes=None):
+    if distance_slopes is None:
+        return _masked_attention_tables(self, q, k_cache, v_cache, meta, H, KV, D, V, scale, block_size, window, sink, sink_values,
+                                        distance_bias, distance_bias_by_head)
+    far = int(max(meta.seg_kv_len.tolist()))                       # the slopes as a table of every distance that occurs
+    table = -torch.arange(far + 1, dtype=torch.float32)[:, None] * distance_slopes.float()[None, :]
+    if distance_bias is not None:
+        table = table + distance_bias[torch.arange(far + 1).clamp(max=distance_bias.shape[0] - 1)]
+    return _masked_attention_tables(self, q, k_cache, v_cache, meta, H, KV, D, V, scale, block_size, window, sink, sink_values, table, None)
+
+
+_route_topk_simple = _route_topk_scored
+
+
+def _route_topk_grouped(self, h, router, correction, top, groups, score="softmax", extra_rows=0, group_score="max", renormalise=False,
+                        weight_eps=0.0, route_scale=1.0, explicit=False):
+    if group_score == "max" and not renormalise and route_scale == 1.0 and not explicit:
+        if score == "softmax" and not extra_rows:
+            return _plain_route_topk(self, h, router, correction, top, groups)
+        return _route_topk_simple(self, h, router, correction, top, groups, score, extra_rows)
+    E = router.shape[0] - extra_rows
+    logits = h.float() @ router.float().T
+    extra = logits[:, E:].contiguous() if extra_rows else None
+    s = torch.sigmoid(logits[:, :E]) if score == "sigmoid" else torch.softmax(logits[:, :E], dim=-1)
+    choice = s if correction is None else s + correction.float()
+    if groups:
+        count, keep = groups
+        per = E // count
+        grouped = choice.view(-1, count, per)
+        rank = grouped.max(-1).values if group_score == "max" else grouped.topk(min(2, per), dim=-1).values.sum(-1)
+        best = torch.sort(rank, dim=-1, descending=True, stable=True).indices[:, :keep]
+        allowed = torch.zeros_like(rank, dtype=torch.bool).scatter_(1, best, True).repeat_interleave(per, dim=1)
+        choice = choice.masked_fill(~allowed, float("-inf"))
+    idx = torch.sort(choice, dim=-1, descending=True, stable=True).indices[:, :top]
+    w = s.gather(1, idx)
+    if renormalise:
+        w = w / (w.sum(-1, keepdim=True) + weight_eps)
+    return idx.to(torch.int32), w * route_scale, extra
+
+
+def _route_topk_any(self, h, router, correction, top, groups, score=None, extra_rows=0, **options):
+    if score is None and not options:
+        return _plain_route_topk(self, h, router, correction, top, groups)
+    return _route_topk_grouped(self, h, router, correction, top, groups, score or "softmax", extra_rows, explicit=True, **options)
+
+
 _stream_rmsnorm, _masked_attention, _route_topk, _expert_ffn = _stream_rmsnorm_gated, _masked_attention_biased, _route_topk_scored, _expert_ffn_general
+_latent_prepare, _head_gate, _unit_qk_cache, _masked_attention, _route_topk = _latent_prepare_general, _head_gate_optional, _unit_qk_cache_general, _masked_attention_sloped, _route_topk_any
 
 
 for _name, _fn in list(globals().items()):
@@ -625,5 +777,6 @@ for _name, _fn in list(globals().items()):
                                                "embed_stream", "cast_rows", "out_rmsnorm_add", "stream_rmsnorm", "unit_qk_cache", "masked_attention",
                                                "retention_scan", "route_topk", "clamped_glu", "expert_ffn",
                                                "embed_bigram_stream", "short_conv", "general_delta_prepare", "general_delta_scan", "matrix_memory",
-                                               "selective_scan", "dual_rmsnorm_mix", "bias_act", "softcap"):
+                                               "selective_scan", "dual_rmsnorm_mix", "bias_act", "softcap",
+                                               "embed_scaled_stream", "stream_rmsnorm_pair", "rows_rmsnorm", "bias_glu", "scale_logits"):
         setattr(TorchRefOps, _name[1:], _fn)
