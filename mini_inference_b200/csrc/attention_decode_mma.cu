@@ -88,9 +88,11 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
                        const int* __restrict__ block_table, const int* __restrict__ table_rows, int table_stride,
                        int H, int KV, int ps, float scale_log2, int window, int* __restrict__ merge_counters,
                        int* __restrict__ error_word, int cluster_merge, int block, int sink,
-                       const float* __restrict__ sink_values, const float* __restrict__ bias_t, int bias_last) {
+                       const float* __restrict__ sink_values, const float* __restrict__ bias_t, int bias_last,
+                       const float* __restrict__ slopes) {
     // BIAS: bias_t float32 [H, bias_last + 1] is added to the scaled score by the distance len - 1 - key (beyond bias_last: the last
-    // entry), one row per head; sink_values float32 [H] (or null: 0) is the score of the sink.
+    // entry), one row per head; sink_values float32 [H] (or null: 0) is the score of the sink; slopes float32 [H] (or null):
+    // slopes[h] * distance is taken off the scaled score as well.
     // block > 0: the query (position len - 1) sees only the keys of its own block of positions, from floor((len - 1) / block) * block on.
     // sink != 0: the softmax has one more term of score 0 that carries no value; ONE warp of ONE split starts its running maximum
     // at 0 and its running sum at 1, and the merges of warps and of splits carry the term along like any other.
@@ -183,6 +185,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     const int head0 = kvh * G + min(g, G - 1), head1 = kvh * G + min(g + 8, G - 1);        // rows beyond G are padding
     const float* __restrict__ bias_row0 = BIAS ? bias_t + (size_t)head0 * (bias_last + 1) : nullptr;
     const float* __restrict__ bias_row1 = BIAS ? bias_t + (size_t)head1 * (bias_last + 1) : nullptr;
+    const float slope0 = BIAS && slopes ? slopes[head0] * LOG2E : 0.f, slope1 = BIAS && slopes ? slopes[head1] * LOG2E : 0.f;
     float m0 = has_sink ? (BIAS && sink_values ? sink_values[head0] * LOG2E : 0.f) : -INFINITY;
     float m1 = has_sink ? (BIAS && sink_values ? sink_values[head1] * LOG2E : 0.f) : -INFINITY;
     float l0 = has_sink && c == 0 ? 1.f : 0.f, l1 = l0;                                    // rows g and g + 8; sums are per thread
@@ -271,9 +274,9 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
                 const int key = blk * 16 + nt * 8 + 2 * c + e;
                 const bool ok = key >= lo && key < len;
                 if (BIAS) {
-                    const int dist = min(max(len - 1 - key, 0), bias_last);
-                    sc[nt][e] = ok ? fmaf(sc[nt][e], scale_log2, bias_row0[dist] * LOG2E) : -INFINITY;
-                    sc[nt][2 + e] = ok ? fmaf(sc[nt][2 + e], scale_log2, bias_row1[dist] * LOG2E) : -INFINITY;
+                    const int far = max(len - 1 - key, 0), dist = min(far, bias_last);
+                    sc[nt][e] = ok ? fmaf(sc[nt][e], scale_log2, fmaf(-slope0, (float)far, bias_row0[dist] * LOG2E)) : -INFINITY;
+                    sc[nt][2 + e] = ok ? fmaf(sc[nt][2 + e], scale_log2, fmaf(-slope1, (float)far, bias_row1[dist] * LOG2E)) : -INFINITY;
                 } else {
                     sc[nt][e] = ok ? sc[nt][e] * scale_log2 : -INFINITY;
                     sc[nt][2 + e] = ok ? sc[nt][2 + e] * scale_log2 : -INFINITY;
@@ -549,7 +552,8 @@ static int decode_mma_rows_launch(const void* q, int q_stride, const void* k_cac
                                   const int* table_rows, int table_stride, int H, int KV, int D, int ps, int splits,
                                   float scale, int window, int* merge_counters, int* error_word, int cache_pages,
                                   int cluster_merge, cudaStream_t stream, int block = 0, int sink = 0,
-                                  const float* sink_values = nullptr, const float* bias_t = nullptr, int bias_last = 0) {
+                                  const float* sink_values = nullptr, const float* bias_t = nullptr, int bias_last = 0,
+                                  const float* slopes = nullptr) {
     if (num_decode == 0) return 0;
     if ((D != 64 && D != 128) || H % KV || H / KV > 16 || ps % 16 || q_stride % 8) return -2;
     dim3 grid(num_decode, KV, splits);
@@ -606,7 +610,7 @@ static int decode_mma_rows_launch(const void* q, int q_stride, const void* k_cac
         return (int)cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<DD, BB, WW, SPLIT, BIAS>, kmap, vmap, \
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
             (__nv_bfloat16*)out, o_part, lse_part, decode_segs, seg_q_start, seg_kv_len, block_table, table_rows, \
-            table_stride, H, KV, ps, scale_log2, window, merge_counters, error_word, use_cluster, block, sink, sink_values, bias_t, bias_last); } while (0)
+            table_stride, H, KV, ps, scale_log2, window, merge_counters, error_word, use_cluster, block, sink, sink_values, bias_t, bias_last, slopes); } while (0)
     if (D == 128) { if (alone) LAUNCH(128, true, DEC_WARPS_ALONE); else if (bulk) LAUNCH(128, true, DEC_WARPS); else LAUNCH(128, false, DEC_WARPS); }
     else { if (alone) LAUNCH(64, true, DEC_WARPS_ALONE); else if (bulk) LAUNCH(64, true, DEC_WARPS); else LAUNCH(64, false, DEC_WARPS); }
 #undef LAUNCH
@@ -655,5 +659,18 @@ MI_EXPORT int mi_attn_decode_mma_rows_biased(const void* q, int q_stride, const 
                                              int bias_last, cudaStream_t stream) {
     if (!bias_t) return -2;
     return decode_mma_rows_launch<true, true>(DECODE_ROWS_ARGS, block, sink, sink_values, bias_t, bias_last);
+}
+
+// The biased form with a slope per head (slopes float32 [H]): slopes[h] * distance is taken off the scaled score, beside the table
+// (a table of one zero per head, bias_last 0, when there is none).
+MI_EXPORT int mi_attn_decode_mma_rows_sloped(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                             float* o_part, float* lse_part, const int* decode_segs, int num_decode,
+                                             const int* seg_q_start, const int* seg_kv_len, const int* block_table,
+                                             const int* table_rows, int table_stride, int H, int KV, int D, int ps, int splits,
+                                             float scale, int window, int* merge_counters, int* error_word, int cache_pages,
+                                             int cluster_merge, int block, int sink, const float* sink_values, const float* bias_t,
+                                             int bias_last, const float* slopes, cudaStream_t stream) {
+    if (!bias_t || !slopes) return -2;
+    return decode_mma_rows_launch<true, true>(DECODE_ROWS_ARGS, block, sink, sink_values, bias_t, bias_last, slopes);
 }
 #undef DECODE_ROWS_ARGS

@@ -56,7 +56,8 @@ __device__ __forceinline__ float bf16_rest(float x) { return x - __bfloat162floa
 // SPLIT: every softmax weight enters the P V product as TWO bfloat16 numbers, its rounding and what the rounding left behind
 // (16 mantissa bits in all, summed in float32), for designs that want their attention weights in more than 16-bit precision.
 // BIAS: a learned number per head and distance, bias_t float32 [H, bias_last + 1] (distances beyond bias_last read the last entry),
-// is added to the scaled score; sink_values float32 [H] (with sink != 0) is the sink's score instead of 0.
+// is added to the scaled score; sink_values float32 [H] (with sink != 0) is the sink's score instead of 0; slopes float32 [H]
+// (or null): slopes[h] * distance is taken off the scaled score as well (a straight line beside, or instead of, the table).
 template <int D, bool SPLIT, bool BIAS>
 __global__ void __launch_bounds__(PF_WARPS * 32, 3)
 attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_cache,
@@ -64,7 +65,8 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                         const int* __restrict__ tiles, const int* __restrict__ seg_q_start,
                         const int* __restrict__ seg_pos0, const int* __restrict__ block_table,
                         const int* __restrict__ table_rows, int table_stride, int H, int KV, int ps, float scale_log2, int window,
-                        int block, int sink, const float* __restrict__ sink_values, const float* __restrict__ bias_t, int bias_last) {
+                        int block, int sink, const float* __restrict__ sink_values, const float* __restrict__ bias_t, int bias_last,
+                        const float* __restrict__ slopes) {
     // block > 0: a query at p sees only keys of its own block of positions, j >= floor(p / block) * block.  sink: the softmax has
     // one more term of score 0 without a value: the running maximum starts at 0 and the running sum at 1.
     auto first_key = [&](int p) { return max(block > 0 ? p / block * block : 0, window > 0 ? p - window + 1 : 0); };
@@ -120,6 +122,8 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     constexpr float LOG2E = 1.4426950408889634f;
     const float sink_score = BIAS && sink && sink_values ? sink_values[h] * LOG2E : 0.f;          // scores are kept in base 2
     const float* __restrict__ bias_row = BIAS ? bias_t + (size_t)h * (bias_last + 1) : nullptr;
+    const float slope_log2 = BIAS && slopes ? slopes[h] * LOG2E : 0.f;        // slopes: slopes[h] * distance is taken off the scaled score
+    auto bias_at = [&](int dist) { return fmaf(-slope_log2, (float)dist, bias_row[min(dist, bias_last)] * LOG2E); };
     float m0 = sink ? sink_score : -INFINITY, m1 = m0, l0 = sink && c == 0 ? 1.f : 0.f, l1 = l0;      // a row's sum is spread over four lanes
     const int p_row0 = pos0 + r0 + warp * 16 + g, p_row1 = p_row0 + 8;     // positions of this thread's two rows
 
@@ -161,8 +165,8 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int j = kt * BK + nt * 8 + 2 * c + e;
-                        s[nt][e] = fmaf(s[nt][e], scale_log2, bias_row[min(p_row0 - j, bias_last)] * LOG2E);
-                        s[nt][2 + e] = fmaf(s[nt][2 + e], scale_log2, bias_row[min(p_row1 - j, bias_last)] * LOG2E);
+                        s[nt][e] = fmaf(s[nt][e], scale_log2, bias_at(p_row0 - j));
+                        s[nt][2 + e] = fmaf(s[nt][2 + e], scale_log2, bias_at(p_row1 - j));
                     }
                 } else {
 #pragma unroll
@@ -180,8 +184,8 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                     const bool ok0 = j <= p_row0 && j >= lo_row0;
                     const bool ok1 = j <= p_row1 && j >= lo_row1;
                     if (BIAS) {
-                        s[nt][e] = ok0 ? fmaf(s[nt][e], scale_log2, bias_row[min(p_row0 - j, bias_last)] * LOG2E) : -INFINITY;
-                        s[nt][2 + e] = ok1 ? fmaf(s[nt][2 + e], scale_log2, bias_row[min(p_row1 - j, bias_last)] * LOG2E) : -INFINITY;
+                        s[nt][e] = ok0 ? fmaf(s[nt][e], scale_log2, bias_at(p_row0 - j)) : -INFINITY;
+                        s[nt][2 + e] = ok1 ? fmaf(s[nt][2 + e], scale_log2, bias_at(p_row1 - j)) : -INFINITY;
                     } else {
                         s[nt][e] = ok0 ? s[nt][e] * scale_log2 : -INFINITY;
                         s[nt][2 + e] = ok1 ? s[nt][2 + e] * scale_log2 : -INFINITY;
@@ -255,7 +259,8 @@ static int prefill_mma_launch(const void* q, int q_stride, const void* k_cache, 
                               const int* tiles, int num_tiles, const int* seg_q_start, const int* seg_pos0,
                               const int* block_table, const int* table_rows, int table_stride, int H, int KV, int D, int ps,
                               int tile_rows, float scale, int window, int block, int sink, cudaStream_t stream,
-                              const float* sink_values = nullptr, const float* bias_t = nullptr, int bias_last = 0) {
+                              const float* sink_values = nullptr, const float* bias_t = nullptr, int bias_last = 0,
+                              const float* slopes = nullptr) {
     if (num_tiles == 0) return 0;
     if ((D != 64 && D != 128) || H % KV || tile_rows != BQ || q_stride % 8) return -2;
     static bool configured[2] = {false, false};
@@ -270,7 +275,7 @@ static int prefill_mma_launch(const void* q, int q_stride, const void* k_cache, 
         } \
         attn_prefill_mma_kernel<DD, SPLIT, BIAS><<<grid, PF_WARPS * 32, smem, stream>>>( \
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
-            (__nv_bfloat16*)out, tiles, seg_q_start, seg_pos0, block_table, table_rows, table_stride, H, KV, ps, scale_log2, window, block, sink, sink_values, bias_t, bias_last); \
+            (__nv_bfloat16*)out, tiles, seg_q_start, seg_pos0, block_table, table_rows, table_stride, H, KV, ps, scale_log2, window, block, sink, sink_values, bias_t, bias_last, slopes); \
     } while (0)
     if (D == 128) LAUNCH(128, 0); else LAUNCH(64, 1);
 #undef LAUNCH
@@ -313,4 +318,17 @@ MI_EXPORT int mi_attn_prefill_mma_biased(const void* q, int q_stride, const void
     if (!bias_t) return -2;
     return prefill_mma_launch<true, true>(q, q_stride, k_cache, v_cache, out, tiles, num_tiles, seg_q_start, seg_pos0, block_table, table_rows,
                                           table_stride, H, KV, D, ps, tile_rows, scale, window, block, sink, stream, sink_values, bias_t, bias_last);
+}
+
+// The biased form with a slope per head (slopes float32 [H]): slopes[h] * distance is taken off the scaled score, beside the table
+// (a table of one zero per head, bias_last 0, when there is none).
+MI_EXPORT int mi_attn_prefill_mma_sloped(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
+                                         const int* tiles, int num_tiles, const int* seg_q_start, const int* seg_pos0,
+                                         const int* block_table, const int* table_rows, int table_stride, int H, int KV, int D, int ps,
+                                         int tile_rows, float scale, int window, int block, int sink, const float* sink_values,
+                                         const float* bias_t, int bias_last, const float* slopes, cudaStream_t stream) {
+    if (!bias_t || !slopes) return -2;
+    return prefill_mma_launch<true, true>(q, q_stride, k_cache, v_cache, out, tiles, num_tiles, seg_q_start, seg_pos0, block_table, table_rows,
+                                          table_stride, H, KV, D, ps, tile_rows, scale, window, block, sink, stream, sink_values, bias_t, bias_last,
+                                          slopes);
 }

@@ -842,7 +842,7 @@ class CudaOps:
         coef, every = q_temp if q_temp else (0.0, 0)
         _check(self.lib.mi_normed_qk_cache(_p(p), p.stride(0), _p(source), 0 if source is None else source.stride(0), _p(lam if source is not None else None),
                                            _p(meta.slots), _p(k_cache), _p(v_cache), T, H, KV, D, V, meta.page_size,
-                                           _c.c_float(eps or 0.0), int(eps is not None), _p(q_weight), _p(k_weight), _p(meta.positions),
+                                           _c.c_float(eps or 0.0), int(eps is not None), _p(q_weight), _p(k_weight), _p(meta.positions if q_temp else None),
                                            _c.c_float(coef), int(every), int(bool(values_are_keys)), _code(p.dtype), self._stream()), "unit_qk_cache")
         self.launches += 1
         return p[:, :H * D]
@@ -876,14 +876,17 @@ class CudaOps:
                 _p(meta.seg_pos0), _p(meta.block_table), _p(rows), meta.max_pages, H, KV, D, meta.page_size, meta.tile,
                 _c.c_float(scale), win, blk, int(bool(sink)), self._stream()), "attn_prefill_mma_masked")
             self.launches += 1
-        elif (num_tiles and slopes is None and self.fast_attention and self.biased_attention_tc and q.dtype == torch.bfloat16 and D == V and D in (64, 128)
+        elif (num_tiles and self.fast_attention and self.biased_attention_tc and q.dtype == torch.bfloat16 and D == V and D in (64, 128)
                 and meta.tile == 64 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
             # the same kernel with the learned sink's score and the distance table (one row per head) in its softmax
             bias_t = self._bias_rows_by_head(distance_bias, distance_bias_by_head, H, q.device)
-            _check(self.lib.mi_attn_prefill_mma_biased(
-                _p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(meta.prefill_tiles), num_tiles, _p(meta.seg_q_start),
-                _p(meta.seg_pos0), _p(meta.block_table), _p(rows), meta.max_pages, H, KV, D, meta.page_size, meta.tile,
-                _c.c_float(scale), win, blk, int(bool(sink)), _p(sink_values), _p(bias_t), bias_t.shape[1] - 1, self._stream()), "attn_prefill_mma_biased")
+            args = (_p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(meta.prefill_tiles), num_tiles, _p(meta.seg_q_start),
+                    _p(meta.seg_pos0), _p(meta.block_table), _p(rows), meta.max_pages, H, KV, D, meta.page_size, meta.tile,
+                    _c.c_float(scale), win, blk, int(bool(sink)), _p(sink_values), _p(bias_t), bias_t.shape[1] - 1)
+            if slopes is None:
+                _check(self.lib.mi_attn_prefill_mma_biased(*args, self._stream()), "attn_prefill_mma_biased")
+            else:                                          # a slope per head times the distance, beside (or instead of) the table
+                _check(self.lib.mi_attn_prefill_mma_sloped(*args, _p(slopes), self._stream()), "attn_prefill_mma_sloped")
             self.launches += 1
         elif num_tiles:
             _check(self.lib.mi_masked_prefill(
@@ -895,7 +898,7 @@ class CudaOps:
             return out
         reach = meta.max_kv_len if not blk else min(meta.max_kv_len, blk)              # the most keys a decoded token can see
         reach = reach if not win else min(reach, win)
-        if ((plain or self.biased_attention_tc) and slopes is None and self.fast_attention and q.dtype == torch.bfloat16 and D == V and D in (64, 128) and H // KV <= 16
+        if ((plain or self.biased_attention_tc) and self.fast_attention and q.dtype == torch.bfloat16 and D == V and D in (64, 128) and H // KV <= 16
                 and meta.page_size % 16 == 0 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
             # the tensor-core decode kernel (the G query heads of a kv head are the rows of one tile), split weights
             S = self.choose_splits(num_decode * KV, reach, 2 if self.bulk_decode else 3, cluster=self.bulk_decode and self.cluster_merge, head_dim=D)
@@ -916,8 +919,12 @@ class CudaOps:
                 _check(self.lib.mi_attn_decode_mma_rows_masked(*args, self._stream()), "attn_decode_mma_masked")
             else:                                          # the learned sink's score and the distance table (one row per head) in the softmax
                 bias_t = self._bias_rows_by_head(distance_bias, distance_bias_by_head, H, q.device)
-                _check(self.lib.mi_attn_decode_mma_rows_biased(*args, _p(sink_values), _p(bias_t), bias_t.shape[1] - 1, self._stream()),
-                       "attn_decode_mma_biased")
+                if slopes is None:
+                    _check(self.lib.mi_attn_decode_mma_rows_biased(*args, _p(sink_values), _p(bias_t), bias_t.shape[1] - 1, self._stream()),
+                           "attn_decode_mma_biased")
+                else:
+                    _check(self.lib.mi_attn_decode_mma_rows_sloped(*args, _p(sink_values), _p(bias_t), bias_t.shape[1] - 1, _p(slopes), self._stream()),
+                           "attn_decode_mma_sloped")
             self.launches += 1
             if S > 1 and counters is None:
                 _check(self.lib.mi_attn_decode_merge(_p(o_part), _p(lse), _p(out), _p(meta.decode_segs), num_decode,

@@ -46,10 +46,10 @@ class LatentAttention(Part):
         else:
             specs = [WeightSpec("q", (H * (D + R), hid))]
         specs += [WeightSpec("dkv", (C + R, hid)), WeightSpec("dkv.norm", (C,), kind="vector", init="norm"),
-                  WeightSpec("uk", (H * D, C)), WeightSpec("uv", (H * V, C)), WeightSpec("o", (hid, H * V))]
+                  WeightSpec("uk", (H * D, C)), WeightSpec("uv", (H * V, C))]
         if self.gate:
             specs.append(WeightSpec("g", (H, hid)))
-        return specs
+        return specs + [WeightSpec("o", (hid, H * V))]
 
     def cache_need(self):
         return KVCacheNeed(1, self.C + self.R, None, planes=1)

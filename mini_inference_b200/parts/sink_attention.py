@@ -70,9 +70,10 @@ class SinkAttention(Part):
 
     def weight_specs(self):
         H, KV, D, V, hid = self.H, self.KV, self.D, self.V, self.hidden
-        specs = [WeightSpec("q", (H * D, hid)), WeightSpec("k", (KV * D, hid)), WeightSpec("o", (hid, H * V))]
+        specs = [WeightSpec("q", (H * D, hid)), WeightSpec("k", (KV * D, hid))]
         if not self.values_are_keys:
             specs.append(WeightSpec("v", (KV * V, hid)))
+        specs.append(WeightSpec("o", (hid, H * V)))
         if self.norm_weights:
             specs += [WeightSpec("q.norm", (D,), kind="vector", init="norm"), WeightSpec("k.norm", (D,), kind="vector", init="norm")]
         if self.value_mix:                                  # a source layer's checkpoint holds the number too; it is not used
