@@ -277,7 +277,7 @@ def reference_arm(args):
 
 
 def design_bench(args):
-    """--design naditar | namesun | nununex: prompt and decode throughput of that design at layer sizes of real models (random weights),
+    """--design naditar | namesun | nununex | megovik: prompt and decode throughput of that design at layer sizes of real models (random weights),
     beside Qwen3 dense of the same width, depth, vocabulary and feed-forward parameters, and every new kernel beside its
     Qwen3 counterpart with its share of the bound it is up against.  One JSON line; the default workload is untouched."""
     import torch
@@ -321,8 +321,8 @@ def design_bench(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--design", default=None, choices=["naditar", "namesun", "nununex"],
-                    help="instead of the default workload: this design beside the closest one the engine had (Qwen3; for nununex: Namesun) at equal sizes")
+    ap.add_argument("--design", default=None, choices=["naditar", "namesun", "nununex", "megovik"],
+                    help="instead of the default workload: this design beside the closest one the engine had (Qwen3; for nununex and megovik: Namesun) at equal sizes")
     ap.add_argument("--design-sizes", default="2k,4k")
     ap.add_argument("--design-layers", type=int, default=8)
     ap.add_argument("--gpus", type=int, default=1)

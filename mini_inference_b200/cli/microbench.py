@@ -682,14 +682,159 @@ def bench_nununex(args, ops, peak, out=print):
     return rows
 
 
+MEGOVIK_SIZES = {
+    # the widths, heads, experts and active feed-forward parameters of NAMESUN_SIZES; latent rows of 128 entries, a query latent of 3/8 of the width
+    "2k": dict(width=2048, ff=8192, heads=16, kv_heads=8, dim=128, l_heads=16, l_dim=64, l_vdim=64, rank=128, q_rank=768, experts=32, top=4, eff=1024, groups=(8, 4)),
+    "4k": dict(width=4096, ff=12288, heads=32, kv_heads=8, dim=128, l_heads=32, l_dim=64, l_vdim=64, rank=128, q_rank=1536, experts=64, top=6, eff=1536, groups=(8, 4)),
+}
+
+
+def megovik_config(size, layers, vocab=65536):
+    z = MEGOVIK_SIZES[size]
+    experts = {"kind": "moe", "expert": {"ff": z["eff"]},
+               "router": {"experts": z["experts"], "top": z["top"], "scale": 2.5, "groups": {"count": z["groups"][0], "keep": z["groups"][1]}}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    lat = {"heads": z["l_heads"], "dim": z["l_dim"], "vdim": z["l_vdim"], "kv_rank": z["rank"], "scale": z["l_dim"] ** -0.5}
+    att = {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+                                          "q_temp": {"coef": 0.1, "every": 1024}}}
+    pattern = [dict(type="latent_attention", mixer=lat, mlp=dense), dict(type="latent_attention", mixer=lat, mlp=experts), dict(att, mlp=experts),
+               dict(type="latent_attention_2", mixer=dict(lat, q_rank=z["q_rank"]), mlp=experts)]
+    return {"architecture": "Megovik", "vocab": vocab, "width": z["width"], "max_positions": 8192, "norm": {"eps": 1e-6}, "embedding": {"scale": z["width"] ** 0.5},
+            "logit_scale": 0.5, "layers": [pattern[i % 4] for i in range(layers)]}
+
+
+def namesun_config_like_megovik(size, layers, vocab=65536):
+    """Namesun (float32 stream, attention with a mask chosen by constants, routed experts with groups) of the same width, depth, vocabulary,
+    attention heads and experts: the closest design the engine already serves."""
+    return namesun_config(size, layers, vocab)
+
+
+def bench_megovik(args, ops, peak, out=print):
+    """Each kernel that the Megovik design added or widened, at the layer sizes of --design-size, beside the like kernel of Namesun (of Naditar
+    for latent attention), with the bytes or operations it cannot avoid as a share of its bound: the measured copy bandwidth or the measured
+    bf16 peak."""
+    import numpy as np
+    z = MEGOVIK_SIZES[args.design_size]
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    bf16_peak = 1590.0
+    if os.path.isfile(os.path.join(here, "MEASURED_PEAKS.json")):
+        with open(os.path.join(here, "MEASURED_PEAKS.json")) as f:
+            bf16_peak = json.load(f)["bf16_tflops"]
+    rows = []
+
+    def line(kernel, shape, us, amount, bound):
+        got, top, unit = {"hbm": (amount / us / 1e3, peak, "GB/s"), "bf16": (amount / us / 1e6, bf16_peak, "TFLOP/s")}[bound]
+        rows.append({"kernel": kernel, "shape": shape, "us": round(us, 2), "achieved": round(got, 2), "unit": unit, "frac": round(got / top, 3)})
+        out(f"{kernel:52s} {shape:46s} {us:9.2f} us {got:9.2f} {unit:10s} {100 * got / top:5.1f} % of bound", flush=True)
+
+    t = lambda a: torch.tensor(np.asarray(a, dtype=np.int32), device="cuda")       # noqa: E731
+    bf = torch.bfloat16
+    W, T, it = z["width"], args.tokens, args.iters
+    rb = lambda *s: torch.randn(*s, device="cuda", dtype=bf)                       # noqa: E731
+    rf = lambda *s: torch.randn(*s, device="cuda")                                 # noqa: E731
+    # ---- stream kernels
+    x, a, b = rf(4, T, W), rb(4, T, W), rb(4, T, W)
+    wn, bias, pre = torch.ones(W, device="cuda"), rf(W), rf(T, W)
+    us = timed(lambda i: ops.stream_rmsnorm_pair(x[i % 4], a[i % 4], b[i % 4], bias, None, wn, 1e-6, None, bf), it)
+    line("pair addition + norm (f32 stream)", f"T={T} width={W}", us, T * W * 14.0, "hbm")
+    us = timed(lambda i: ops.stream_rmsnorm_pair(x[i % 4], a[i % 4], b[i % 4], bias, pre, wn, 1e-6, None, bf), it)
+    line("pair addition + embedded tokens + norm", f"T={T} width={W}", us, T * W * 18.0, "hbm")
+    us = timed(lambda i: ops.out_rmsnorm_add(x[i % 4], a[i % 4], wn, wn, 0.3, 1e-6, bf), it)
+    line("  Namesun: output norm + add (f32 stream)", f"T={T} width={W}", us, T * W * 12.0, "hbm")
+    ids = torch.randint(0, 65536, (T,), device="cuda", dtype=torch.int32)
+    table, ptab, pos = rb(65536, W), rb(8192, W), t(np.arange(T) % 8192)
+    us = timed(lambda i: ops.embed_scaled_stream(ids, table, 45.0, ptab, pos), it)
+    line("embedding * scale + position row", f"T={T} width={W}", us, T * W * 8.0, "hbm")
+    us = timed(lambda i: ops.embed_stream(ids, table, bf), it)
+    line("  Namesun: embedding", f"T={T} width={W}", us, T * W * 8.0, "hbm")
+    del table, ptab
+    F = z["ff"]
+    gu, gb = rb(2, T, 2 * F), rf(2 * F)
+    us = timed(lambda i: ops.bias_glu(gu[i % 2], gb, "relu"), it)
+    line("biases + relu gate", f"T={T} ff={F}", us, T * F * 6.0, "hbm")
+    us = timed(lambda i: ops.clamped_glu(gu[i % 2], 7.0, 1.702), it)
+    line("  Namesun: clamped gate", f"T={T} ff={F}", us, T * F * 6.0, "hbm")
+    del gu
+    cq, wq = rb(T, z["q_rank"] + z["rank"]), torch.ones(z["q_rank"], device="cuda")
+    us = timed(lambda i: ops.rows_rmsnorm(cq[:, :z["q_rank"]], wq, 1e-6), it)
+    line("norm of the query latent", f"T={T} q_rank={z['q_rank']}", us, T * z["q_rank"] * 4.0, "hbm")
+    # ---- attention with weighted norms, a temperature, keys as values and distance slopes, beside Namesun's masked attention
+    H, KV, D, page = z["heads"], z["kv_heads"], z["dim"], args.page_size if hasattr(args, "page_size") else 16
+    slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], device="cuda")
+    qw = torch.ones(D, device="cuda")
+    for B, n, ctx in ((1, T, T), (8, 1, args.ctx), (64, 1, args.ctx)):
+        pages_per = -(-ctx // page)
+        n_pages = B * pages_per + 1
+        kc, vc = rb(n_pages, KV, page, D), rb(n_pages, KV, page, D)
+        table = t(np.arange(1, n_pages).reshape(B, pages_per))
+        tiles = [(s, r) for s in range(B) for r in range(0, n, 64)] if n > 1 else []
+        meta = types.SimpleNamespace(seg_q_start=t(np.arange(B + 1) * n), seg_pos0=t([ctx - n] * B), seg_kv_len=t([ctx] * B), table_rows=t(np.arange(B)),
+                                     block_table=table, max_pages=pages_per, page_size=page, decode_segs=t(np.arange(B) if n == 1 else []),
+                                     prefill_tiles=t(tiles).view(-1, 2), tile=64, max_kv_len=ctx,
+                                     slots=t((np.arange(B)[:, None] * pages_per * page + page + ctx - n + np.arange(n)[None, :]).reshape(-1)),
+                                     positions=t(np.tile(np.arange(ctx - n, ctx), B)))
+        Tn = B * n
+        p2, p3 = rb(Tn, (H + KV) * D), rb(Tn, (H + 2 * KV) * D)
+        us = timed(lambda i: ops.unit_qk_cache(p2, H, KV, D, D, 1e-6, None, None, meta, kc, vc, q_weight=qw, k_weight=qw, q_temp=(0.1, 1024), values_are_keys=True), it)
+        line("q/k norm * weight, temperature, k -> both pools", f"rows={Tn} H={H} KV={KV} D={D}", us, Tn * ((2 * H + 3 * KV) * D) * 2.0, "hbm")
+        us = timed(lambda i: ops.unit_qk_cache(p3, H, KV, D, D, 1e-6, None, None, meta, kc, vc), it)
+        line("  Namesun: unit q/k, k and v -> pools", f"rows={Tn} H={H} KV={KV} D={D}", us, Tn * ((2 * H + 4 * KV) * D) * 2.0, "hbm")
+        q = p2[:, :H * D]
+        if n > 1:
+            amount, bound = 4.0 * H * D * (n * (n + 1) / 2) * B, "bf16"
+        else:
+            amount, bound = B * ctx * KV * D * 2 * 2.0, "hbm"
+        us = timed(lambda i: ops.masked_attention(q, kc, vc, meta, H, KV, D, D, D ** -0.5, None, None, False, distance_slopes=slopes), it)
+        line("attention with distance slopes", f"B={B} rows={n} keys={ctx} H={H} KV={KV} D={D}", us, amount, bound)
+        us = timed(lambda i: ops.masked_attention(q, kc, vc, meta, H, KV, D, D, D ** -0.5, None, None, True), it)
+        line("  Namesun: attention with a sink (no block)", f"B={B} rows={n} keys={ctx} H={H} KV={KV} D={D}", us, amount, bound)
+        # latent attention without a rotated part: the cached row is key and value of every head
+        LH, C = z["l_heads"], z["rank"]
+        lc = rb(n_pages, 1, page, C)
+        ql = rb(Tn, LH, C)
+        if n > 1:
+            amount, bound = 4.0 * LH * C * (n * (n + 1) / 2) * B, "bf16"
+        else:
+            amount, bound = B * ctx * C * 2.0, "hbm"
+        us = timed(lambda i: ops.latent_attention(ql, lc, meta, LH, C, 0, 0.125), it)
+        line("latent attention (row = key = value)", f"B={B} rows={n} keys={ctx} H={LH} C={C}", us, amount, bound)
+        del kc, vc, lc
+    # ---- routed feed-forward: sigmoid router with groups ranked by two scores and renormalised weights; experts weighted on their output
+    E, top, Fe, groups = z["experts"], z["top"], z["eff"], z["groups"]
+    for rows_n in (T, 64, 8):
+        h = rb(rows_n, W)
+        router, corr = rb(E, W) * 0.05, torch.zeros(E, device="cuda")
+        reps = 4 if rows_n > 64 else max(2, (300 << 20) // (E * 3 * Fe * W * 2) + 1)
+        w_in, w_out = rb(reps, E, 2 * Fe, W) * 0.02, rb(reps, E, W, Fe) * 0.02
+        us = timed(lambda i: ops.route_topk(h, router, None, top, groups, score="sigmoid", group_score="top2_sum", renormalise=True, weight_eps=1e-20,
+                                            route_scale=2.5), it)
+        line("router: sigmoid, groups by two scores, renormalised", f"rows={rows_n} experts={E} top={top}", us, rows_n * W * 2.0 + E * W * 2.0, "hbm")
+        us = timed(lambda i: ops.route_topk(h, router, corr, top, groups), it)
+        line("  Namesun: router (softmax, groups by one score)", f"rows={rows_n} experts={E} top={top}", us, rows_n * W * 2.0 + E * W * 2.0, "hbm")
+        chosen, wts, _ = ops.route_topk(h, router, None, top, groups, score="sigmoid", group_score="top2_sum", renormalise=True, weight_eps=1e-20, route_scale=2.5)
+        flops, hit = 2.0 * rows_n * top * 3 * Fe * W, min(E, rows_n * top)
+        amount, bound = (flops, "bf16") if rows_n > 64 else (hit * 3.0 * Fe * W * 2, "hbm")
+        us = timed(lambda i: ops.expert_ffn(h, chosen, wts, w_in[i % reps], w_out[i % reps], float("inf"), 1.0, None, up_shift=0.0), it)
+        line("experts (silu gate), weighted on their output", f"rows={rows_n} experts={E} top={top} ff={Fe}", us, amount, bound)
+        us = timed(lambda i: ops.expert_ffn(h, chosen, wts, w_in[i % reps], w_out[i % reps], 7.0, 1.702, None), it)
+        line("  Namesun: experts (clamped gate)", f"rows={rows_n} experts={E} top={top} ff={Fe}", us, amount, bound)
+        del w_in, w_out
+    lo = rf(64, 65536)
+    us = timed(lambda i: ops.scale_logits(lo, 0.5), it)
+    line("scale of the logits", "rows=64 vocab=65536", us, 64 * 65536 * 8.0, "hbm")
+    ops.check_errors()
+    return rows
+
+
 DESIGNS = {"naditar": (naditar_config, qwen3_config_like, bench_design), "namesun": (namesun_config, qwen3_config_like_namesun, bench_namesun),
-           "nununex": (nununex_config, namesun_config_like_nununex, bench_nununex)}
-BESIDE = {"nununex": "namesun"}            # the design an entry of DESIGNS is set beside (default: qwen3)
+           "nununex": (nununex_config, namesun_config_like_nununex, bench_nununex),
+           "megovik": (megovik_config, namesun_config_like_megovik, bench_megovik)}
+BESIDE = {"nununex": "namesun", "megovik": "namesun"}            # the design an entry of DESIGNS is set beside (default: qwen3)
 
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("what", choices=["gemm", "attention", "prefill", "design", "namesun", "nununex"])
+    ap.add_argument("what", choices=["gemm", "attention", "prefill", "design", "namesun", "nununex", "megovik"])
     ap.add_argument("--design-size", default="2k", choices=sorted(NADITAR_SIZES), help="design: layer sizes of the Naditar kernels")
     ap.add_argument("--size", default="4b", choices=sorted(SIZES))
     ap.add_argument("--rows", default="1,8,64", type=lambda s: [int(v) for v in s.split(",")])
@@ -708,7 +853,7 @@ def main(argv=None):
     ops = get_ops("cuda:0")
     peak, src = peak_gbs()
     print(f"# peak {peak} GB/s ({src})")
-    {"gemm": bench_gemm, "attention": bench_attention, "prefill": bench_prefill_attention, "design": bench_design, "namesun": bench_namesun, "nununex": bench_nununex}[args.what](args, ops, peak)
+    {"gemm": bench_gemm, "attention": bench_attention, "prefill": bench_prefill_attention, "design": bench_design, "namesun": bench_namesun, "nununex": bench_nununex, "megovik": bench_megovik}[args.what](args, ops, peak)
     return 0
 
 

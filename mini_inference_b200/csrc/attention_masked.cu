@@ -241,13 +241,15 @@ MI_EXPORT int mi_normed_qk_cache(void* p, int ldp, const void* v_src, int ld_src
                                  cudaStream_t stream) {
     if (T_ == 0) return 0;
     if ((v_is_k && (Dv != D || v_src)) || (temp_every > 0 && !positions) || ((q_w == nullptr) != (k_w == nullptr))) return -2;
+    // few tokens (decode steps): a warp per head, so that no warp walks several heads one after the other
+    const int nt = T_ >= 256 ? 128 : min(1024, max(128, 32 * (H + KV)));
     if (dtype == MI_BF16)
-        unit_qk_cache_kernel<__nv_bfloat16><<<T_, 128, 0, stream>>>((__nv_bfloat16*)p, ldp, (const __nv_bfloat16*)v_src, ld_src, lam, slots,
+        unit_qk_cache_kernel<__nv_bfloat16><<<T_, nt, 0, stream>>>((__nv_bfloat16*)p, ldp, (const __nv_bfloat16*)v_src, ld_src, lam, slots,
                                                                     (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, H, KV, D, Dv, ps, eps, unit,
                                                                     q_w, k_w, positions, temp_coef, temp_every, v_is_k);
     else
-        unit_qk_cache_kernel<float><<<T_, 128, 0, stream>>>((float*)p, ldp, (const float*)v_src, ld_src, lam, slots, (float*)k_cache,
-                                                            (float*)v_cache, H, KV, D, Dv, ps, eps, unit, q_w, k_w, positions, temp_coef,
+        unit_qk_cache_kernel<float><<<T_, nt, 0, stream>>>((float*)p, ldp, (const float*)v_src, ld_src, lam, slots, (float*)k_cache,
+                                                           (float*)v_cache, H, KV, D, Dv, ps, eps, unit, q_w, k_w, positions, temp_coef,
                                                             temp_every, v_is_k);
     return (int)cudaGetLastError();
 }

@@ -75,6 +75,70 @@ __global__ void stream_rmsnorm_pair_kernel(float* __restrict__ x, const TD* __re
     }
 }
 
+// The same with the row held in registers between the statistic and the output: four neighbouring entries per thread and step
+// (16-byte loads of the stream, 8- or 16-byte loads of the outputs), VPT steps per thread; hidden = 4 * k, k <= NT * VPT.
+template <typename TD> __device__ __forceinline__ float4 load4(const TD* p) {
+    if constexpr (sizeof(TD) == 4) {
+        return *reinterpret_cast<const float4*>(p);
+    } else {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u), __uint_as_float(raw.y << 16),
+                           __uint_as_float(raw.y & 0xffff0000u));
+    }
+}
+template <typename TY> __device__ __forceinline__ void store4(TY* p, float4 v) {
+    if constexpr (sizeof(TY) == 4) {
+        *reinterpret_cast<float4*>(p) = v;
+    } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<uint32_t*>(&lo);
+        raw.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+}
+
+template <typename TD, typename TY, int VPT>
+__global__ void __launch_bounds__(NT) stream_rmsnorm_pair_vec_kernel(float* __restrict__ x, const TD* __restrict__ a, const TD* __restrict__ b,
+                                                                     const float* __restrict__ bias, const float* __restrict__ pre, long long pre_stride,
+                                                                     const float* __restrict__ w, TY* __restrict__ y, const int* __restrict__ rows,
+                                                                     int hidden, float eps) {
+    __shared__ float scratch[32];
+    const size_t r = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
+    float* xr = x + r * hidden;
+    const TD* ar = a ? a + r * hidden : nullptr;
+    const TD* br = b ? b + r * hidden : nullptr;
+    const float* pr = pre ? pre + r * pre_stride : nullptr;
+    const int quads = hidden >> 2;
+    float4 v[VPT];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int i = (threadIdx.x + k * NT) * 4;
+        if (threadIdx.x + k * NT < quads) {
+            float4 xv = *reinterpret_cast<const float4*>(xr + i), d = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (ar) d = load4<TD>(ar + i);
+            if (br) { const float4 t = load4<TD>(br + i); d.x += t.x; d.y += t.y; d.z += t.z; d.w += t.w; }
+            if (bias) { const float4 t = *reinterpret_cast<const float4*>(bias + i); d.x += t.x; d.y += t.y; d.z += t.z; d.w += t.w; }
+            if (pr) { const float4 t = *reinterpret_cast<const float4*>(pr + i); xv.x += t.x; xv.y += t.y; xv.z += t.z; xv.w += t.w; }
+            xv.x += d.x; xv.y += d.y; xv.z += d.z; xv.w += d.w;             // the order of pair_sum: (a + b + bias), the pre-addition, the stream
+            v[k] = xv;
+            ss += xv.x * xv.x + xv.y * xv.y + xv.z * xv.z + xv.w * xv.w;
+        }
+    }
+    const float s = rsqrtf(block_sum<NT>(ss, scratch) / hidden + eps);
+    TY* yr = y + (size_t)blockIdx.x * hidden;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int i = (threadIdx.x + k * NT) * 4;
+        if (threadIdx.x + k * NT < quads) {
+            if (!rows) *reinterpret_cast<float4*>(xr + i) = v[k];
+            const float4 wv = *reinterpret_cast<const float4*>(w + i);
+            store4<TY>(yr + i, make_float4(v[k].x * s * wv.x, v[k].y * s * wv.y, v[k].z * s * wv.z, v[k].w * s * wv.w));
+        }
+    }
+}
+
 template <typename T>
 __global__ void rows_rmsnorm_kernel(const T* __restrict__ x, long long ldx, const float* __restrict__ w, T* __restrict__ y, int cols, float eps) {
     __shared__ float scratch[32];
@@ -122,12 +186,16 @@ __global__ void bias_glu_vec_kernel(const T* __restrict__ gu, const float* __res
         float gv[VN], uv[VN], r[VN];
         load16(g + i, gv);
         load16(g + inter + i, uv);
+        if (bias) {                                        // the halves of the bias start on 16 bytes as the halves of the row do
 #pragma unroll
-        for (int e = 0; e < VN; ++e) {
-            float a = gv[e], u = uv[e];
-            if (bias) { a += bias[i + e]; u += bias[inter + i + e]; }
-            r[e] = glu_act(a, act) * u;
+            for (int e = 0; e < VN; e += 4) {
+                const float4 bg = *reinterpret_cast<const float4*>(bias + i + e), bu = *reinterpret_cast<const float4*>(bias + inter + i + e);
+                gv[e] += bg.x; gv[e + 1] += bg.y; gv[e + 2] += bg.z; gv[e + 3] += bg.w;
+                uv[e] += bu.x; uv[e + 1] += bu.y; uv[e + 2] += bu.z; uv[e + 3] += bu.w;
+            }
         }
+#pragma unroll
+        for (int e = 0; e < VN; ++e) r[e] = glu_act(gv[e], act) * uv[e];
         store16v(o + i, r);
     }
 }
@@ -156,13 +224,21 @@ MI_EXPORT int mi_stream_rmsnorm_pair(float* x, const void* a, const void* b, con
                                      const float* w, void* y, const int* rows, int n, int hidden, float eps, int d_dtype, int y_dtype,
                                      cudaStream_t stream) {
     if (n == 0) return 0;
-#define GO(TD, TY) stream_rmsnorm_pair_kernel<TD, TY><<<n, NT, 0, stream>>>(x, (const TD*)a, (const TD*)b, bias, pre, pre_stride, w, (TY*)y, rows, hidden, eps)
+    auto aligned = [](const void* p) { return ((uintptr_t)p % 16) == 0; };
+    const int quads = hidden / 4;
+    const int vpt = quads <= NT ? 1 : quads <= 2 * NT ? 2 : quads <= 4 * NT ? 4 : quads <= 8 * NT ? 8 : 0;
+    const bool vec = hidden % 4 == 0 && vpt && aligned(x) && aligned(a) && aligned(b) && aligned(bias) && aligned(pre) && aligned(w) && aligned(y) &&
+                     (pre_stride % 4) == 0;
+#define GOV(TD, TY, V) stream_rmsnorm_pair_vec_kernel<TD, TY, V><<<n, NT, 0, stream>>>(x, (const TD*)a, (const TD*)b, bias, pre, pre_stride, w, (TY*)y, rows, hidden, eps)
+#define GO(TD, TY) do { if (!vec) stream_rmsnorm_pair_kernel<TD, TY><<<n, NT, 0, stream>>>(x, (const TD*)a, (const TD*)b, bias, pre, pre_stride, w, (TY*)y, rows, hidden, eps); \
+        else if (vpt == 1) GOV(TD, TY, 1); else if (vpt == 2) GOV(TD, TY, 2); else if (vpt == 4) GOV(TD, TY, 4); else GOV(TD, TY, 8); } while (0)
     if (d_dtype == MI_BF16 && y_dtype == MI_BF16) GO(__nv_bfloat16, __nv_bfloat16);
     else if (d_dtype == MI_F32 && y_dtype == MI_F32) GO(float, float);
     else if (d_dtype == MI_F32 && y_dtype == MI_BF16) GO(float, __nv_bfloat16);
     else if (d_dtype == MI_BF16 && y_dtype == MI_F32) GO(__nv_bfloat16, float);
     else return -1;
 #undef GO
+#undef GOV
     return (int)cudaGetLastError();
 }
 
@@ -178,7 +254,7 @@ MI_EXPORT int mi_bias_glu(const void* gu, const float* bias, void* out, int rows
     if (rows == 0) return 0;
     if (act < 0 || act > 2) return -2;
     const int vn = dtype == MI_BF16 ? 8 : 4;
-    const bool vec = inter % vn == 0 && ((uintptr_t)gu % 16) == 0 && ((uintptr_t)out % 16) == 0;
+    const bool vec = inter % vn == 0 && ((uintptr_t)gu % 16) == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)bias % 16) == 0;
     const int per = vec ? NT * vn : NT;
     dim3 grid(rows, rows >= 512 ? 1 : min(16, (inter + per - 1) / per));
 #define GO(T) do { if (vec) bias_glu_vec_kernel<T><<<grid, NT, 0, stream>>>((const T*)gu, bias, (T*)out, inter, act); \

@@ -752,7 +752,14 @@ class CudaOps:
         # weights' precision where the design wants it; their output has C + R columns per head, of which the first C count.
         if (q.dtype == torch.bfloat16 and Dk in (64, 128) and meta.tile == 64 and self.fast_attention and meta.page_size % 16 == 0
                 and q.data_ptr() % 16 == 0):
-            o = self.paged_attention(q.view(T, H * Dk), cache, cache, meta, H, 1, Dk, scale, None, split_weights=True)
+            if H <= 16 or not num_decode:
+                o = self.paged_attention(q.view(T, H * Dk), cache, cache, meta, H, 1, Dk, scale, None, split_weights=True)
+            else:
+                # the decode kernel takes up to 16 query heads per key head as the rows of its tile: more heads go in groups of 16
+                # (each group reads the cached rows once; the rows are small next to what the heads' weights cost)
+                qv = q.view(T, H * Dk)
+                o = torch.cat([self.paged_attention(qv[:, h0 * Dk:min(h0 + 16, H) * Dk], cache, cache, meta, min(16, H - h0), 1, Dk, scale, None,
+                                                    split_weights=True) for h0 in range(0, H, 16)], dim=1)
             return o.view(T, H, Dk)[:, :, :C].permute(1, 0, 2)
         out = torch.empty((H, T, C), dtype=q.dtype, device=q.device)
         buf, hs, ts = out, T * C, C
