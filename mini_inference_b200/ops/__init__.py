@@ -703,9 +703,10 @@ class CudaOps:
         return out
 
     # ---------------------------------------------------------------- latent attention
-    def batched_linear(self, x, col0, head_stride, K, w):
+    def batched_linear(self, x, col0, head_stride, K, w, side_by_side=False):
         """One product per head: w [H, N, K]; x is [T, ...] with head h's K inputs at columns col0 + h * head_stride
-        (col0 given), or [H, T, K].  Returns [H, T, N].  bfloat16: the library's batched product; float32: this
+        (col0 given), or [H, T, K].  Returns [H, T, N], or with side_by_side [T, H N] (the heads' outputs laid side by side in
+        each token's row, written there by the products themselves).  bfloat16: the library's batched product; float32: this
         package's float32 product, head by head (no reduced-precision mode)."""
         H, N, _ = w.shape
         if col0 is not None:
@@ -713,13 +714,20 @@ class CudaOps:
             xs = torch.as_strided(x, (H, T, K), (head_stride, x.stride(0), 1), x.storage_offset() + col0)
         else:
             T, xs = x.shape[1], x
+        if side_by_side:
+            rows = torch.empty((T, H * N), dtype=x.dtype, device=x.device)
+            out = rows.view(T, H, N).transpose(0, 1)                     # [H, T, N] with a row stride of H N
         if x.dtype != torch.float32:
+            if side_by_side:
+                torch.bmm(xs, w.transpose(1, 2), out=out)
+                return rows
             return torch.bmm(xs, w.transpose(1, 2))
-        out = torch.empty((H, T, N), dtype=torch.float32, device=x.device)
+        if not side_by_side:
+            out = torch.empty((H, T, N), dtype=torch.float32, device=x.device)
         for h in range(H):
-            _check(self.lib.mi_gemm_f32_nt(_p(xs[h]), xs.stride(1), _p(w[h]), _p(out[h]), N, T, N, K, self._stream()), "gemm_f32")
+            _check(self.lib.mi_gemm_f32_nt(_p(xs[h]), xs.stride(1), _p(w[h]), _p(out[h]), out.stride(1), T, N, K, self._stream()), "gemm_f32")
         self.launches += H
-        return out
+        return rows if side_by_side else out
 
     def latent_prepare(self, p, q_abs, H, D, R, C, norm_w, eps, inv_freq, meta, cache, q_rows=None, dkv_col=None):
         """p [T, ..] = q heads [H, D + R] | dkv [C + R] | ..; q_abs [H, T, C].  Returns q [T, H, C + R] = [q_abs | rotated

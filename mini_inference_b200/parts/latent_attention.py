@@ -99,6 +99,8 @@ class LatentAttention(Part):
                                    cache.k if owns_cache else None)                # [T, H, C + R]; [c | kr] -> the pages
             gate_col = H * (D + R) + C + R
         o_lat = ops.latent_attention(q, cache.k, meta, H, C, R, self.scale)        # [H, T, C]
+        if not self.gate:                                                          # no gate: the products write the heads side by side
+            return ops.batched_linear(o_lat, None, None, C, self.uv, side_by_side=True), self.o
         o = ops.batched_linear(o_lat, None, None, C, self.uv)                      # [H, T, V]
-        rows = ops.head_gate(o, p[:, gate_col:] if self.gate else None, ctx.dtype)  # [T, H V]
+        rows = ops.head_gate(o, p[:, gate_col:], ctx.dtype)                        # [T, H V]
         return rows, self.o

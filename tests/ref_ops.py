@@ -218,11 +218,12 @@ def _delta_scan(self, prep, H, KV, D, V, state, batch):
     return o
 
 
-def _batched_linear(self, x, col0, head_stride, K, w):
+def _batched_linear(self, x, col0, head_stride, K, w, side_by_side=False):
     H = w.shape[0]
     if col0 is not None:
         x = torch.stack([x[:, col0 + h * head_stride:col0 + h * head_stride + K] for h in range(H)])
-    return torch.einsum("htk,hnk->htn", x.float(), w.float()).to(x.dtype)
+    out = torch.einsum("htk,hnk->htn", x.float(), w.float()).to(x.dtype)
+    return out.transpose(0, 1).reshape(out.shape[1], -1).contiguous() if side_by_side else out
 
 
 def _rotate_pairs(v, positions, inv_freq):
