@@ -820,3 +820,17 @@ def test_trace_run_program_on_gpu(dirs, tmp_path):
         g0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(64, -1))
         g1 = torch.from_numpy(np.fromfile(out / "1.f32", dtype="<f4").reshape(6, -1))
         assert_close(torch.cat([g0, g1]), want, TOL[dtype])
+
+
+@gpu
+def test_run_engine_command_line_on_gpu(dirs, tmp_path):
+    """The serving command line on a model folder of this design: the scheduler, temperature sampling and CUDA graphs."""
+    d, cfg, page = dirs["mix"]
+    out = tmp_path / "m.json"
+    r = subprocess.run([os.path.join(ROOT, "bin", "run_engine"), "--model", d, "--dtype", "bfloat16", "-n", "5", "-c", "3", "--warmup", "1",
+                        "--max-new-tokens", "9", "--prompt-len", "5:30", "--kv-tokens", "512", "--page-size", str(page), "--temperature", "0.8",
+                        "--cuda-graphs", "on", "--out", str(out)], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    data = json.loads(out.read_text())
+    assert data["summary"]["engine"]["architecture"] == "Megovik"
+    assert all(run["generated_tokens"] == 9 and run["error"] is None for run in data["runs"])
