@@ -183,8 +183,8 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     const bool has_sink = sink && s == 0 && warp == 0;
     constexpr float LOG2E = 1.4426950408889634f;
     const int head0 = kvh * G + min(g, G - 1), head1 = kvh * G + min(g + 8, G - 1);        // rows beyond G are padding
-    const float* __restrict__ bias_row0 = BIAS ? bias_t + (size_t)head0 * (bias_last + 1) : nullptr;
-    const float* __restrict__ bias_row1 = BIAS ? bias_t + (size_t)head1 * (bias_last + 1) : nullptr;
+    const float* __restrict__ bias_row0 = BIAS && bias_t ? bias_t + (size_t)head0 * (bias_last + 1) : nullptr;     // no table: slopes alone
+    const float* __restrict__ bias_row1 = BIAS && bias_t ? bias_t + (size_t)head1 * (bias_last + 1) : nullptr;
     const float slope0 = BIAS && slopes ? slopes[head0] * LOG2E : 0.f, slope1 = BIAS && slopes ? slopes[head1] * LOG2E : 0.f;
     float m0 = has_sink ? (BIAS && sink_values ? sink_values[head0] * LOG2E : 0.f) : -INFINITY;
     float m1 = has_sink ? (BIAS && sink_values ? sink_values[head1] * LOG2E : 0.f) : -INFINITY;
@@ -275,8 +275,9 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
                 const bool ok = key >= lo && key < len;
                 if (BIAS) {
                     const int far = max(len - 1 - key, 0), dist = min(far, bias_last);
-                    sc[nt][e] = ok ? fmaf(sc[nt][e], scale_log2, fmaf(-slope0, (float)far, bias_row0[dist] * LOG2E)) : -INFINITY;
-                    sc[nt][2 + e] = ok ? fmaf(sc[nt][2 + e], scale_log2, fmaf(-slope1, (float)far, bias_row1[dist] * LOG2E)) : -INFINITY;
+                    const float t0 = bias_row0 ? bias_row0[dist] * LOG2E : 0.f, t1 = bias_row1 ? bias_row1[dist] * LOG2E : 0.f;
+                    sc[nt][e] = ok ? fmaf(sc[nt][e], scale_log2, fmaf(-slope0, (float)far, t0)) : -INFINITY;
+                    sc[nt][2 + e] = ok ? fmaf(sc[nt][2 + e], scale_log2, fmaf(-slope1, (float)far, t1)) : -INFINITY;
                 } else {
                     sc[nt][e] = ok ? sc[nt][e] * scale_log2 : -INFINITY;
                     sc[nt][2 + e] = ok ? sc[nt][2 + e] * scale_log2 : -INFINITY;
@@ -662,7 +663,7 @@ MI_EXPORT int mi_attn_decode_mma_rows_biased(const void* q, int q_stride, const 
 }
 
 // The biased form with a slope per head (slopes float32 [H]): slopes[h] * distance is taken off the scaled score, beside the table
-// (a table of one zero per head, bias_last 0, when there is none).
+// (bias_t null: no table).
 MI_EXPORT int mi_attn_decode_mma_rows_sloped(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
                                              float* o_part, float* lse_part, const int* decode_segs, int num_decode,
                                              const int* seg_q_start, const int* seg_kv_len, const int* block_table,
@@ -670,7 +671,7 @@ MI_EXPORT int mi_attn_decode_mma_rows_sloped(const void* q, int q_stride, const 
                                              float scale, int window, int* merge_counters, int* error_word, int cache_pages,
                                              int cluster_merge, int block, int sink, const float* sink_values, const float* bias_t,
                                              int bias_last, const float* slopes, cudaStream_t stream) {
-    if (!bias_t || !slopes) return -2;
+    if (!slopes) return -2;                                // bias_t may be null: slopes alone
     return decode_mma_rows_launch<true, true>(DECODE_ROWS_ARGS, block, sink, sink_values, bias_t, bias_last, slopes);
 }
 #undef DECODE_ROWS_ARGS

@@ -121,9 +121,9 @@ attn_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     for (int t = 0; t < DT; ++t) { o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f; }
     constexpr float LOG2E = 1.4426950408889634f;
     const float sink_score = BIAS && sink && sink_values ? sink_values[h] * LOG2E : 0.f;          // scores are kept in base 2
-    const float* __restrict__ bias_row = BIAS ? bias_t + (size_t)h * (bias_last + 1) : nullptr;
+    const float* __restrict__ bias_row = BIAS && bias_t ? bias_t + (size_t)h * (bias_last + 1) : nullptr;      // no table: slopes alone
     const float slope_log2 = BIAS && slopes ? slopes[h] * LOG2E : 0.f;        // slopes: slopes[h] * distance is taken off the scaled score
-    auto bias_at = [&](int dist) { return fmaf(-slope_log2, (float)dist, bias_row[min(dist, bias_last)] * LOG2E); };
+    auto bias_at = [&](int dist) { return fmaf(-slope_log2, (float)dist, bias_row ? bias_row[min(dist, bias_last)] * LOG2E : 0.f); };
     float m0 = sink ? sink_score : -INFINITY, m1 = m0, l0 = sink && c == 0 ? 1.f : 0.f, l1 = l0;      // a row's sum is spread over four lanes
     const int p_row0 = pos0 + r0 + warp * 16 + g, p_row1 = p_row0 + 8;     // positions of this thread's two rows
 
@@ -321,13 +321,13 @@ MI_EXPORT int mi_attn_prefill_mma_biased(const void* q, int q_stride, const void
 }
 
 // The biased form with a slope per head (slopes float32 [H]): slopes[h] * distance is taken off the scaled score, beside the table
-// (a table of one zero per head, bias_last 0, when there is none).
+// (bias_t null: no table).
 MI_EXPORT int mi_attn_prefill_mma_sloped(const void* q, int q_stride, const void* k_cache, const void* v_cache, void* out,
                                          const int* tiles, int num_tiles, const int* seg_q_start, const int* seg_pos0,
                                          const int* block_table, const int* table_rows, int table_stride, int H, int KV, int D, int ps,
                                          int tile_rows, float scale, int window, int block, int sink, const float* sink_values,
                                          const float* bias_t, int bias_last, const float* slopes, cudaStream_t stream) {
-    if (!bias_t || !slopes) return -2;
+    if (!slopes) return -2;                                // bias_t may be null: slopes alone
     return prefill_mma_launch<true, true>(q, q_stride, k_cache, v_cache, out, tiles, num_tiles, seg_q_start, seg_pos0, block_table, table_rows,
                                           table_stride, H, KV, D, ps, tile_rows, scale, window, block, sink, stream, sink_values, bias_t, bias_last,
                                           slopes);

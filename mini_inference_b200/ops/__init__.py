@@ -894,10 +894,11 @@ class CudaOps:
         elif (num_tiles and self.fast_attention and self.biased_attention_tc and q.dtype == torch.bfloat16 and D == V and D in (64, 128)
                 and meta.tile == 64 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
             # the same kernel with the learned sink's score and the distance table (one row per head) in its softmax
-            bias_t = self._bias_rows_by_head(distance_bias, distance_bias_by_head, H, q.device)
+            no_table = slopes is not None and distance_bias is None and distance_bias_by_head is None        # slopes alone: the kernel reads no table
+            bias_t = None if no_table else self._bias_rows_by_head(distance_bias, distance_bias_by_head, H, q.device)
             args = (_p(q), q.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(meta.prefill_tiles), num_tiles, _p(meta.seg_q_start),
                     _p(meta.seg_pos0), _p(meta.block_table), _p(rows), meta.max_pages, H, KV, D, meta.page_size, meta.tile,
-                    _c.c_float(scale), win, blk, int(bool(sink)), _p(sink_values), _p(bias_t), bias_t.shape[1] - 1)
+                    _c.c_float(scale), win, blk, int(bool(sink)), _p(sink_values), _p(bias_t), 0 if no_table else bias_t.shape[1] - 1)
             if slopes is None:
                 _check(self.lib.mi_attn_prefill_mma_biased(*args, self._stream()), "attn_prefill_mma_biased")
             else:                                          # a slope per head times the distance, beside (or instead of) the table
@@ -933,11 +934,14 @@ class CudaOps:
             if plain:
                 _check(self.lib.mi_attn_decode_mma_rows_masked(*args, self._stream()), "attn_decode_mma_masked")
             else:                                          # the learned sink's score and the distance table (one row per head) in the softmax
-                bias_t = self._bias_rows_by_head(distance_bias, distance_bias_by_head, H, q.device)
                 if slopes is None:
+                    bias_t = self._bias_rows_by_head(distance_bias, distance_bias_by_head, H, q.device)
                     _check(self.lib.mi_attn_decode_mma_rows_biased(*args, _p(sink_values), _p(bias_t), bias_t.shape[1] - 1, self._stream()),
                            "attn_decode_mma_biased")
+                elif distance_bias is None and distance_bias_by_head is None:                 # slopes alone: the kernel reads no table
+                    _check(self.lib.mi_attn_decode_mma_rows_sloped(*args, _p(sink_values), _p(None), 0, _p(slopes), self._stream()), "attn_decode_mma_sloped")
                 else:
+                    bias_t = self._bias_rows_by_head(distance_bias, distance_bias_by_head, H, q.device)
                     _check(self.lib.mi_attn_decode_mma_rows_sloped(*args, _p(sink_values), _p(bias_t), bias_t.shape[1] - 1, _p(slopes), self._stream()),
                            "attn_decode_mma_sloped")
             self.launches += 1
